@@ -61,12 +61,20 @@ def load_model_config(source: str | Path | Mapping[str, Any]):
         if not path.is_file():
             raise FileNotFoundError(f"no config.json at {path}")
         raw = json.loads(path.read_text())
+    entry = get_architecture(architecture_name(raw))
+    return entry, entry.config_class.from_dict(raw)
+
+
+def architecture_name(raw: Mapping[str, Any]) -> str:
+    """The design a config.json names: the one entry of ``architectures``, or, in files that have
+    no such list, the string under ``architecture``."""
     architectures = raw.get("architectures")
+    if architectures is None and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
     if not isinstance(architectures, (list, tuple)) or len(architectures) != 1:
         raise ValueError(
             f"config.json: 'architectures' must list exactly one name, got {architectures!r}")
-    entry = get_architecture(architectures[0])
-    return entry, entry.config_class.from_dict(raw)
+    return architectures[0]
 
 
 def _load_builtin() -> None:

@@ -1,0 +1,283 @@
+// Paged causal attention whose positions enter as a bias on the scores instead of a rotation, with
+// keys and values of sizes of their own, in float32 arithmetic throughout (scores, softmax weights
+// and the weighted sum of the values), for float32 and bfloat16 projections and pages.
+//
+//   head_norm_scale_cache   per-head RMSNorm of queries and keys (one weight vector for all heads),
+//                           queries multiplied by a temperature that grows with the position,
+//                           1 + coef * ln(floor((p + 1) / every) + 1); keys and values into their pages
+//   biased_paged_attention  score(i, j) = q_i . k_j * scale - slope_h * (i - j), softmax over j <= i
+//                           (and j > i - window where there is one)
+//
+// The attention kernel has the launch shape and the masking of the generic kernel in
+// attention_generic.cu: a block is 16 consecutive queries of one request and one query head, found
+// from the block index alone; keys come through the block table in tiles of 32.
+#include "common.cuh"
+
+namespace b200 {
+
+template <typename T>
+__global__ void head_norm_scale_cache_kernel(
+    const T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
+    const float* __restrict__ q_weight, const float* __restrict__ k_weight, T* __restrict__ q_out,
+    T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int d, int dv, int page_size, float eps,
+    float temp_coef, int temp_every) {
+    const int token = blockIdx.x;
+    const int warps = blockDim.x >> 5;
+    const int head_slot = blockIdx.y * warps + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (head_slot >= nq + 2 * nkv) return;
+    const bool is_q = head_slot < nq;
+    const bool is_k = !is_q && head_slot < nq + nkv;
+    if (!is_q && k_pages == nullptr) return;
+    const size_t row = (size_t)token * ((size_t)(nq + nkv) * d + (size_t)nkv * dv);
+    int slot = 0;
+    if (!is_q) {
+        slot = slots[token];
+        if (slot < 0) return;
+    }
+    const int page = slot / page_size, offset = slot - page * page_size;
+    if (!is_q && !is_k) {
+        const int kv_head = head_slot - nq - nkv;
+        const T* src = qkv + row + (size_t)(nq + nkv) * d + (size_t)kv_head * dv;
+        T* dst = v_pages + (((size_t)page * nkv + kv_head) * page_size + offset) * dv;
+        for (int j = lane; j < dv; j += 32) dst[j] = src[j];
+        return;
+    }
+    const T* src = qkv + row + (size_t)head_slot * d;
+    const float* weight = is_q ? q_weight : k_weight;
+    float factor = 1.0f;
+    if (weight) {
+        float sum_sq = 0.0f;
+        for (int j = lane; j < d; j += 32) {
+            const float v = to_float(src[j]);
+            sum_sq = fmaf(v, v, sum_sq);
+        }
+        factor = rsqrtf(warp_sum(sum_sq) / (float)d + eps);
+    }
+    float temperature = 1.0f;
+    if (is_q && temp_every > 0)
+        temperature = 1.0f + temp_coef * logf((float)((positions[token] + 1) / temp_every) + 1.0f);
+    T* dst = is_q ? q_out + ((size_t)token * nq + head_slot) * d
+                  : k_pages + (((size_t)page * nkv + (head_slot - nq)) * page_size + offset) * d;
+    for (int j = lane; j < d; j += 32) {
+        float v = to_float(src[j]) * factor;
+        if (weight) v *= weight[j];
+        dst[j] = from_float<T>(v * temperature);
+    }
+}
+
+constexpr int kQueryTile = 16;
+constexpr int kKeyTile = 32;
+constexpr int kWarps = 4;
+constexpr int kRowsPerWarp = kQueryTile / kWarps;
+
+template <typename T, int DPL>  // DPL: value elements per lane, dv <= 32 * DPL
+__global__ void __launch_bounds__(kWarps * 32) biased_paged_attention_kernel(
+    const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+    T* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
+    const int* __restrict__ block_table, const float* __restrict__ slopes, int num_requests, int max_pages,
+    int nq, int nkv, int d, int dv, int page_size, float scale, int window) {
+    extern __shared__ float smem[];
+    float* q_s = smem;                                   // [16][d]
+    float* k_s = q_s + kQueryTile * d;                   // [32][d + 1]
+    float* v_s = k_s + kKeyTile * (d + 1);               // [32][dv]
+
+    const int block = blockIdx.x;
+    int lo = 0, hi = num_requests - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (query_start[mid] / kQueryTile + mid <= block) lo = mid; else hi = mid - 1;
+    }
+    const int request = lo;
+    const int q_begin = query_start[request];
+    const int q_len = query_start[request + 1] - q_begin;
+    const int local_tile = block - (q_begin / kQueryTile + request);
+    const int tile_first = local_tile * kQueryTile;
+    if (tile_first >= q_len) return;
+    const int rows_here = min(kQueryTile, q_len - tile_first);
+    const int seq_len = seq_lens[request];
+    const int past = seq_len - q_len;
+    const int head = blockIdx.y;
+    const int kv_head = head / (nq / nkv);
+    const float slope = slopes ? slopes[head] : 0.0f;
+    const int* table = block_table + (size_t)request * max_pages;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    for (int idx = tid; idx < kQueryTile * d; idx += blockDim.x) {
+        const int row = idx / d, j = idx - row * d;
+        float v = 0.0f;
+        if (row < rows_here) v = to_float(q[((size_t)(q_begin + tile_first + row) * nq + head) * d + j]);
+        q_s[idx] = v;
+    }
+
+    float acc[kRowsPerWarp][DPL];
+    float row_max[kRowsPerWarp], row_sum[kRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        row_max[r] = -INFINITY;
+        row_sum[r] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[r][i] = 0.0f;
+    }
+
+    const int first_pos = past + tile_first;
+    const int last_pos = first_pos + rows_here - 1;
+    int key_begin = 0;
+    if (window > 0) key_begin = max(0, first_pos - window + 1);
+    key_begin = (key_begin / kKeyTile) * kKeyTile;
+    const int key_end = last_pos + 1;
+
+    for (int k0 = key_begin; k0 < key_end; k0 += kKeyTile) {
+        __syncthreads();
+        for (int idx = tid; idx < kKeyTile * d; idx += blockDim.x) {
+            const int key = idx / d, j = idx - key * d;
+            const int kp = k0 + key;
+            float kv = 0.0f;
+            if (kp < key_end) {
+                const int page = table[kp / page_size];
+                if (page >= 0) kv = to_float(k_pages[(((size_t)page * nkv + kv_head) * page_size + kp % page_size) * d + j]);
+            }
+            k_s[key * (d + 1) + j] = kv;
+        }
+        for (int idx = tid; idx < kKeyTile * dv; idx += blockDim.x) {
+            const int key = idx / dv, j = idx - key * dv;
+            const int kp = k0 + key;
+            float vv = 0.0f;
+            if (kp < key_end) {
+                const int page = table[kp / page_size];
+                if (page >= 0) vv = to_float(v_pages[(((size_t)page * nkv + kv_head) * page_size + kp % page_size) * dv + j]);
+            }
+            v_s[key * dv + j] = vv;
+        }
+        __syncthreads();
+
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const int row = warp * kRowsPerWarp + r;
+            if (row >= rows_here) continue;                  // uniform within the warp
+            const int q_pos = first_pos + row;
+            const int kp = k0 + lane;
+            const float* q_row = q_s + row * d;
+            const float* k_row = k_s + lane * (d + 1);
+            float score = 0.0f;
+            for (int j = 0; j < d; ++j) score = fmaf(q_row[j], k_row[j], score);
+            score = score * scale - slope * (float)(q_pos - kp);
+            bool visible = kp <= q_pos;
+            if (window > 0) visible = visible && (kp > q_pos - window);
+            if (!visible) score = -INFINITY;
+            const float new_max = fmaxf(row_max[r], warp_max(score));
+            if (new_max == -INFINITY) continue;
+            const float correction = expf(row_max[r] - new_max);
+            const float p = visible ? expf(score - new_max) : 0.0f;
+            row_sum[r] = row_sum[r] * correction + warp_sum(p);
+            row_max[r] = new_max;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) acc[r][i] *= correction;
+            for (int key = 0; key < kKeyTile; ++key) {
+                const float pk = __shfl_sync(0xffffffffu, p, key);
+                const float* v_row = v_s + key * dv;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const int j = lane + 32 * i;
+                    if (j < dv) acc[r][i] = fmaf(pk, v_row[j], acc[r][i]);
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        const int row = warp * kRowsPerWarp + r;
+        if (row >= rows_here) continue;
+        const float inv = row_sum[r] > 0.0f ? 1.0f / row_sum[r] : 0.0f;
+        T* dst = out + ((size_t)(q_begin + tile_first + row) * nq + head) * dv;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int j = lane + 32 * i;
+            if (j < dv) dst[j] = from_float<T>(acc[r][i] * inv);
+        }
+    }
+}
+
+template <typename T, int DPL>
+int launch_biased(const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
+                  const int* seq_lens, const int* block_table, const float* slopes, int num_requests, int num_tokens,
+                  int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale, int window,
+                  cudaStream_t stream) {
+    auto kernel = biased_paged_attention_kernel<T, DPL>;
+    const size_t smem = sizeof(float) * ((size_t)kQueryTile * d + (size_t)kKeyTile * (d + 1) + (size_t)kKeyTile * dv);
+    if (smem > 48 * 1024) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("biased_paged_attention", cudaGetErrorString(status));
+    }
+    dim3 grid(num_tokens / kQueryTile + num_requests, nq);
+    kernel<<<grid, kWarps * 32, smem, stream>>>(
+        (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, query_start, seq_lens, block_table, slopes,
+        num_requests, max_pages, nq, nkv, d, dv, page_size, scale, window);
+    return check_launch("biased_paged_attention");
+}
+
+template <typename T>
+int dispatch_biased(const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
+                    const int* seq_lens, const int* block_table, const float* slopes, int num_requests,
+                    int num_tokens, int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale,
+                    int window, cudaStream_t stream) {
+#define B200_CASE(DPL)                                                                                       \
+    if (dv <= 32 * DPL)                                                                                      \
+        return launch_biased<T, DPL>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes,   \
+                                     num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size, scale,  \
+                                     window, stream);
+    B200_CASE(1) B200_CASE(2) B200_CASE(4) B200_CASE(8) B200_CASE(16)
+#undef B200_CASE
+    return fail("biased_paged_attention", "value heads above 512 are not built");
+}
+
+}  // namespace b200
+
+// qkv rows: [nq * d | nkv * d | nkv * dv].  q_weight / k_weight may be null (no head norm),
+// temp_every <= 0 means no temperature, k_pages / v_pages may be null (nothing is stored).
+// dtype: 0 = float32, 1 = bfloat16.
+B200_EXPORT int b200_head_norm_scale_cache(
+    const void* qkv, const int* positions, const int* slots, const float* q_weight, const float* k_weight,
+    void* q_out, void* k_pages, void* v_pages, int num_tokens, int nq, int nkv, int d, int dv, int page_size,
+    float eps, float temp_coef, int temp_every, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (num_tokens == 0) return 0;
+    if ((k_pages == nullptr) != (v_pages == nullptr))
+        return fail("head_norm_scale_cache", "key and value pages must be given together");
+    if (k_pages && page_size <= 0) return fail("head_norm_scale_cache", "page_size must be positive");
+    const int warps = 4;
+    dim3 grid(num_tokens, (nq + 2 * nkv + warps - 1) / warps);
+    if (grid.y > 65535) return fail("head_norm_scale_cache", "too many heads");
+    if (dtype == 0)
+        head_norm_scale_cache_kernel<float><<<grid, warps * 32, 0, stream>>>(
+            (const float*)qkv, positions, slots, q_weight, k_weight, (float*)q_out, (float*)k_pages, (float*)v_pages,
+            nq, nkv, d, dv, page_size, eps, temp_coef, temp_every);
+    else if (dtype == 1)
+        head_norm_scale_cache_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+            (const __nv_bfloat16*)qkv, positions, slots, q_weight, k_weight, (__nv_bfloat16*)q_out,
+            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, nq, nkv, d, dv, page_size, eps, temp_coef, temp_every);
+    else
+        return fail("head_norm_scale_cache", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("head_norm_scale_cache");
+}
+
+// slopes: float32 [nq] or null (no bias).  window <= 0: every earlier key is visible.
+B200_EXPORT int b200_biased_paged_attention(
+    const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start, const int* seq_lens,
+    const int* block_table, const float* slopes, int num_requests, int num_tokens, int max_pages, int nq, int nkv,
+    int d, int dv, int page_size, float scale, int window, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (num_requests == 0 || num_tokens == 0) return 0;
+    if (nq <= 0 || nkv <= 0 || nq % nkv) return fail("biased_paged_attention", "query heads must be a multiple of key/value heads");
+    if (nq > 65535) return fail("biased_paged_attention", "more than 65535 query heads");
+    if (d <= 0 || dv <= 0 || page_size <= 0 || max_pages <= 0) return fail("biased_paged_attention", "sizes must be positive");
+    if (dtype == 0)
+        return dispatch_biased<float>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes, num_requests,
+                                      num_tokens, max_pages, nq, nkv, d, dv, page_size, scale, window, stream);
+    if (dtype == 1)
+        return dispatch_biased<__nv_bfloat16>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes,
+                                              num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size, scale,
+                                              window, stream);
+    return fail("biased_paged_attention", "dtype must be 0 (float32) or 1 (bfloat16)");
+}

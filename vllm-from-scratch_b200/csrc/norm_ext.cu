@@ -1,0 +1,231 @@
+// RMSNorm forms with a second operand, and the embedding with a bigram table.
+//
+//   add_normed_rmsnorm   residual += rms(x) * x_weight;  out = rms(residual) * weight
+//                        (a norm behind a sublayer, the sum, and the norm in front of the next
+//                        sublayer as one kernel; either half may be left out)
+//   paired_norm_mean     out = (rms(a) * wa + rms(b) * wb) / 2      (two mixers side by side)
+//   gated_group_norm     out = rms_g(y * silu(z)) * w               (gate first, groups of channels)
+//                        out = rms_g(y) * w * sigmoid(z)            (gate behind the norm)
+//   bigram_embedding     residual = embed[id] + bigram[(prev * a + id * b) mod buckets]
+//
+// rms(v) = v * rsqrt(mean(v^2) + eps); every statistic, sum and gate in float32.  One block per
+// row (per row and group for the gated form).
+#include "common.cuh"
+
+namespace b200 {
+
+template <typename T>
+__global__ void add_normed_rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ x_weight, float x_eps,
+                                          float* __restrict__ residual, const float* __restrict__ weight,
+                                          T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int out_row = blockIdx.x;
+    const int row = rows ? rows[out_row] : out_row;
+    const size_t base = (size_t)row * hidden;
+    const bool store = rows == nullptr;
+    float sum_x = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = to_float(x[base + i]);
+        sum_x = fmaf(v, v, sum_x);
+    }
+    const float inv_x = rsqrtf(block_sum(sum_x, scratch) / (float)hidden + x_eps);
+    float sum_sq = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = residual[base + i] + to_float(x[base + i]) * inv_x * x_weight[i];
+        if (store) residual[base + i] = v;
+        sum_sq = fmaf(v, v, sum_sq);
+    }
+    if (out == nullptr) return;
+    const float inv = rsqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
+    const size_t out_base = (size_t)out_row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        // The thread that stored an element reads it back; gathered rows form the sum again.
+        const float v = store ? residual[base + i] : residual[base + i] + to_float(x[base + i]) * inv_x * x_weight[i];
+        out[out_base + i] = from_float<T>(v * inv * weight[i]);
+    }
+}
+
+template <typename T>
+__global__ void paired_norm_mean_kernel(const T* __restrict__ a, const float* __restrict__ wa,
+                                        const T* __restrict__ b, const float* __restrict__ wb,
+                                        T* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float sum_a = 0.0f, sum_b = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float va = to_float(a[base + i]), vb = to_float(b[base + i]);
+        sum_a = fmaf(va, va, sum_a);
+        sum_b = fmaf(vb, vb, sum_b);
+    }
+    const float inv_a = rsqrtf(block_sum(sum_a, scratch) / (float)hidden + eps);
+    const float inv_b = rsqrtf(block_sum(sum_b, scratch) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float va = to_float(a[base + i]) * inv_a * wa[i], vb = to_float(b[base + i]) * inv_b * wb[i];
+        out[base + i] = from_float<T>(0.5f * (va + vb));
+    }
+}
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// GATE_FIRST: v = y * silu(z), out = rms_g(v) * w.  Otherwise out = rms_g(y) * w * sigmoid(z).
+template <typename T, bool GATE_FIRST>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
+                                        const float* __restrict__ weight, T* __restrict__ out, int width,
+                                        int group_width, float eps) {
+    __shared__ float scratch[33];
+    const size_t token = blockIdx.x;
+    const int first = blockIdx.y * group_width;
+    const float* y_row = y + token * width + first;
+    const T* g_row = gate + token * gate_stride + first;
+    float sum_sq = 0.0f;
+    for (int i = threadIdx.x; i < group_width; i += blockDim.x) {
+        float v = y_row[i];
+        if (GATE_FIRST) {
+            const float z = to_float(g_row[i]);
+            v *= z * sigmoid_f(z);
+        }
+        sum_sq = fmaf(v, v, sum_sq);
+    }
+    const float inv = rsqrtf(block_sum(sum_sq, scratch) / (float)group_width + eps);
+    T* o_row = out + token * width + first;
+    for (int i = threadIdx.x; i < group_width; i += blockDim.x) {
+        const float z = to_float(g_row[i]);
+        float v = y_row[i];
+        if (GATE_FIRST) v = v * (z * sigmoid_f(z)) * inv * weight[first + i];
+        else v = v * inv * weight[first + i] * sigmoid_f(z);
+        o_row[i] = from_float<T>(v);
+    }
+}
+
+// One block per token.  The token ahead of a portion's first token is the request's state
+// (`previous[slot]`), which the block of that first token reads and then replaces by the
+// portion's last token: no other block touches the word.
+template <typename T>
+__global__ void bigram_embedding_kernel(const T* __restrict__ table, const T* __restrict__ bigram,
+                                        const int* __restrict__ ids, const int* __restrict__ positions,
+                                        const int* __restrict__ token_request, const int* __restrict__ query_start,
+                                        const int* __restrict__ slots, int* __restrict__ previous,
+                                        float* __restrict__ residual, int hidden, int vocab, int buckets,
+                                        int mul_prev, int mul_cur, int* __restrict__ error_flag) {
+    __shared__ int before_s;
+    const int token = blockIdx.x;
+    const int id = ids[token];
+    if (threadIdx.x == 0) {
+        const int request = token_request[token];
+        const int first = query_start[request];
+        int before = -1;
+        if (token > first) {
+            before = ids[token - 1];
+        } else {
+            const int slot = slots[request];
+            if (positions[token] > 0) before = previous[slot];
+            previous[slot] = ids[query_start[request + 1] - 1];
+        }
+        before_s = before;
+    }
+    __syncthreads();
+    const int before = before_s;
+    float* dst = residual + (size_t)token * hidden;
+    if (id < 0 || id >= vocab || before >= vocab) {
+        if (threadIdx.x == 0) atomicExch(error_flag, token + 1);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.0f;
+        return;
+    }
+    long long row = buckets;                                  // the first token of a sequence: the last row
+    if (before >= 0) row = ((long long)before * mul_prev + (long long)id * mul_cur) % buckets;
+    const T* src = table + (size_t)id * hidden;
+    const T* add = bigram + (size_t)row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]) + to_float(add[i]);
+}
+
+inline int row_threads(int width) {
+    int threads = 64;
+    while (threads < 1024 && threads * 4 < width) threads *= 2;
+    return threads;
+}
+
+}  // namespace b200
+
+// dtype: 0 = float32, 1 = bfloat16 (x and out; residual and weights are float32).  `weight` and
+// `out` may both be null: only the sum is formed.  With `rows` the residual is left as it was.
+B200_EXPORT int b200_add_normed_rmsnorm(const void* x, const float* x_weight, float x_eps, float* residual,
+                                        const float* weight, void* out, const int* rows, int num_rows, int hidden,
+                                        float eps, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (num_rows == 0) return 0;
+    if (num_rows < 0 || hidden <= 0) return fail("add_normed_rmsnorm", "negative row count or width");
+    if ((weight == nullptr) != (out == nullptr)) return fail("add_normed_rmsnorm", "weight and out go together");
+    const int threads = row_threads(hidden);
+    if (dtype == 0)
+        add_normed_rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>(
+            (const float*)x, x_weight, x_eps, residual, weight, (float*)out, rows, hidden, eps);
+    else if (dtype == 1)
+        add_normed_rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+            (const __nv_bfloat16*)x, x_weight, x_eps, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
+    else
+        return fail("add_normed_rmsnorm", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("add_normed_rmsnorm");
+}
+
+B200_EXPORT int b200_paired_norm_mean(const void* a, const float* wa, const void* b, const float* wb, void* out,
+                                      int num_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (num_rows == 0) return 0;
+    if (num_rows < 0 || hidden <= 0) return fail("paired_norm_mean", "negative row count or width");
+    const int threads = row_threads(hidden);
+    if (dtype == 0)
+        paired_norm_mean_kernel<float><<<num_rows, threads, 0, stream>>>(
+            (const float*)a, wa, (const float*)b, wb, (float*)out, hidden, eps);
+    else if (dtype == 1)
+        paired_norm_mean_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+            (const __nv_bfloat16*)a, wa, (const __nv_bfloat16*)b, wb, (__nv_bfloat16*)out, hidden, eps);
+    else
+        return fail("paired_norm_mean", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("paired_norm_mean");
+}
+
+// y: float32 [tokens, width]; gate: rows of `gate_stride` elements of which the first `width` are the
+// gate; groups equal parts of the width, each normalised by its own root mean square.
+B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate_stride, const float* weight,
+                                      void* out, int tokens, int width, int groups, int gate_first, float eps,
+                                      int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (tokens == 0) return 0;
+    if (tokens < 0 || width <= 0 || groups <= 0 || width % groups) return fail("gated_group_norm", "width must divide into the groups");
+    if (groups > 65535) return fail("gated_group_norm", "more than 65535 groups");
+    const int group_width = width / groups;
+    const int threads = row_threads(group_width);
+    dim3 grid(tokens, groups);
+#define B200_CASE(T, FIRST)                                                                             \
+    gated_group_norm_kernel<T, FIRST><<<grid, threads, 0, stream>>>(y, (const T*)gate, gate_stride, weight, \
+                                                                    (T*)out, width, group_width, eps)
+    if (dtype == 0 && gate_first) B200_CASE(float, true);
+    else if (dtype == 0) B200_CASE(float, false);
+    else if (dtype == 1 && gate_first) B200_CASE(__nv_bfloat16, true);
+    else if (dtype == 1) B200_CASE(__nv_bfloat16, false);
+    else return fail("gated_group_norm", "dtype must be 0 (float32) or 1 (bfloat16)");
+#undef B200_CASE
+    return check_launch("gated_group_norm");
+}
+
+B200_EXPORT int b200_bigram_embedding(const void* table, const void* bigram, const int* ids, const int* positions,
+                                      const int* token_request, const int* query_start, const int* slots,
+                                      int* previous, float* residual, int num_tokens, int hidden, int vocab,
+                                      int buckets, int mul_prev, int mul_cur, int* error_flag, int dtype,
+                                      cudaStream_t stream) {
+    using namespace b200;
+    if (num_tokens == 0) return 0;
+    if (buckets <= 0) return fail("bigram_embedding", "buckets must be positive");
+    const int threads = row_threads(hidden);
+    if (dtype == 0)
+        bigram_embedding_kernel<float><<<num_tokens, threads, 0, stream>>>(
+            (const float*)table, (const float*)bigram, ids, positions, token_request, query_start, slots, previous,
+            residual, hidden, vocab, buckets, mul_prev, mul_cur, error_flag);
+    else if (dtype == 1)
+        bigram_embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+            (const __nv_bfloat16*)table, (const __nv_bfloat16*)bigram, ids, positions, token_request, query_start,
+            slots, previous, residual, hidden, vocab, buckets, mul_prev, mul_cur, error_flag);
+    else
+        return fail("bigram_embedding", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("bigram_embedding");
+}

@@ -70,7 +70,7 @@ class DecodeGraphs:
         model, views = self.runner.model, self.runner.storage.views
 
         def body() -> torch.Tensor:
-            x, residual = model.forward(token_ids, ctx, views)
+            x, residual = model.forward(token_ids, ctx, views, embedding_cache=self.runner.storage.embedding_view)
             return model.logits(x, residual, rows)
 
         # Warm-up: kernels compiled and loaded before the capture.  It runs this very batch, and
@@ -188,7 +188,7 @@ class MixedGraphs:
         model, views = self.runner.model, self.runner.storage.views
 
         def body() -> torch.Tensor | None:
-            x, residual = model.forward(token_ids, ctx, views)
+            x, residual = model.forward(token_ids, ctx, views, embedding_cache=self.runner.storage.embedding_view)
             return None if meta["num_wanted"] == 0 else model.logits(x, residual, want_rows)
 
         # A warm-up run of this very body: the step that came before went through the ordinary

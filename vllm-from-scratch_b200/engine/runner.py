@@ -67,7 +67,8 @@ class ModelRunner:
         self.storage = self.manager = self.step_function = None
         cache_from = [entry.cache_from for entry in self.spec.schedule]
         self.storage = CacheStorage(self.model.cache_needs(), cache_from, page_size, num_pages,
-                                    self.max_requests, self.dtype, self.device)
+                                    self.max_requests, self.dtype, self.device,
+                                    embedding_need=self.model.embedding.cache_need())
         self.manager = CacheManager(self.storage.group_windows, page_size, num_pages, self.max_requests,
                                     self.enable_prefix_caching, has_state=self.storage.has_state)
         self.step_function = StepFunction(self.model, self.storage, self.manager)

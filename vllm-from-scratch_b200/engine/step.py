@@ -46,6 +46,7 @@ class StepFunction:
         self.page_size = storage.page_size
         self.last_context: StepContext | None = None     # kept for the packed-inputs trace
         self._validated_shapes: set[tuple[int, int, int]] = set()
+        self.trail: list | None = None                   # set to a list to collect every layer's output of the next steps
 
     # ------------------------------------------------------------------ packing
     def pack_host(self, entries: list[StepEntry], pad_requests: int | None = None,
@@ -169,7 +170,8 @@ class StepFunction:
         shape = (meta["num_tokens"], meta["num_requests"], meta["num_wanted"])
         first_time = shape not in self._validated_shapes
         with kernels.validation(first_time):
-            x, residual = self.model.forward(token_ids, ctx, self.storage.views)
+            x, residual = self.model.forward(token_ids, ctx, self.storage.views,
+                                             embedding_cache=self.storage.embedding_view, trail=self.trail)
             logits = None if meta["num_wanted"] == 0 else self.model.logits(x, residual, want_rows)
         self._validated_shapes.add(shape)
         return logits

@@ -448,3 +448,9 @@ def mask_tokens(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor) 
          _P(_check("logits", logits, torch.float32)), _I(logits.shape[1]),
          _P(_check("rows", rows, torch.int32, (count,))), _P(_check("tokens", tokens, torch.int32, (count,))),
          _I(count), _stream())
+
+
+# ---------------------------------------------------- mixers beyond rotary softmax attention
+from .mixing import (add_normed_rmsnorm, bigram_embedding, biased_paged_attention, causal_conv_silu,  # noqa: E402
+                     decayed_linear_attention, gated_group_norm, head_norm_scale_cache, paired_norm_mean,
+                     selective_scan)

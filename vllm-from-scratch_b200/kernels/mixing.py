@@ -1,0 +1,202 @@
+"""Python face of the kernels for mixers beyond rotary softmax attention and for the norm forms
+that go with them: attention with a distance bias and keys and values of sizes of their own,
+recurrences with a matrix of state per head (decayed linear attention, selective scan), the short
+causal convolution, norms with a second operand, and the embedding with a bigram table.
+
+As everywhere in this package there is no CPU or library alternative behind these functions.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _F, _I, _P, _check, _code, _run, _stream, count_launch
+
+_RUN = (torch.float32, torch.bfloat16)
+
+
+# ------------------------------------------------------------------------ norms
+def add_normed_rmsnorm(x: torch.Tensor, x_weight: torch.Tensor, x_eps: float, residual: torch.Tensor,
+                       weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
+                       rows: torch.Tensor | None = None) -> None:
+    """``residual += rms(x) * x_weight`` in float32, then ``out = rms(residual) * weight`` in
+    ``out``'s dtype (``weight`` and ``out`` both None: the sum only).  With ``rows`` only those rows
+    are formed, written compactly to ``out``, and ``residual`` is left as it was."""
+    tokens, hidden = residual.shape
+    out_rows = tokens if rows is None else rows.shape[0]
+    _run("norm_ext", "b200_add_normed_rmsnorm",
+         _P(_check("normed addend", x, _RUN, (tokens, hidden))),
+         _P(_check("addend norm weight", x_weight, torch.float32, (hidden,))), _F(x_eps),
+         _P(_check("residual", residual, torch.float32)),
+         _P(_check("norm weight", weight, torch.float32, (hidden,), optional=True)),
+         _P(_check("norm output", out, x.dtype, (out_rows, hidden), optional=True)),
+         _P(_check("row index", rows, torch.int32, optional=True)),
+         _I(out_rows), _I(hidden), _F(eps), _I(_code(x.dtype)), _stream())
+
+
+def paired_norm_mean(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, eps: float,
+                     out: torch.Tensor) -> None:
+    """``out = (rms(a) * wa + rms(b) * wb) / 2`` row by row, in float32."""
+    tokens, hidden = a.shape
+    _run("norm_ext", "b200_paired_norm_mean",
+         _P(_check("first branch", a, _RUN, (tokens, hidden))), _P(_check("first weight", wa, torch.float32, (hidden,))),
+         _P(_check("second branch", b, a.dtype, (tokens, hidden))), _P(_check("second weight", wb, torch.float32, (hidden,))),
+         _P(_check("mean output", out, a.dtype, (tokens, hidden))), _I(tokens), _I(hidden), _F(eps),
+         _I(_code(a.dtype)), _stream())
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, groups: int,
+                     gate_first: bool, eps: float) -> None:
+    """``y`` float32 ``[T, W]``; ``gate`` rows whose first W elements are the gate (a view of a
+    wider projection will do: only its row stride is used).  ``gate_first``: ``out = rms_g(y *
+    silu(gate)) * weight``; otherwise ``out = rms_g(y) * weight * sigmoid(gate)``; ``rms_g``
+    normalises each of ``groups`` equal parts of a row by its own root mean square."""
+    tokens, width = y.shape
+    _check("recurrence output", y, torch.float32)
+    _check("gated norm weight", weight, torch.float32, (width,))
+    _check("gated norm output", out, _RUN, (tokens, width))
+    if gate.dtype != out.dtype or gate.dim() != 2 or gate.shape[0] != tokens or gate.shape[1] < width \
+            or gate.stride(1) != 1 or not gate.is_cuda:
+        from . import KernelError
+        raise KernelError(f"gate: shape {tuple(gate.shape)}, strides {gate.stride()}, dtype {gate.dtype}")
+    _run("norm_ext", "b200_gated_group_norm", _P(y.data_ptr()), _P(gate.data_ptr()), _I(gate.stride(0)),
+         _P(weight.data_ptr()), _P(out.data_ptr()), _I(tokens), _I(width), _I(groups), _I(1 if gate_first else 0),
+         _F(eps), _I(_code(out.dtype)), _stream())
+
+
+def bigram_embedding(table: torch.Tensor, bigram: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+                     token_request: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
+                     previous: torch.Tensor, residual: torch.Tensor, mul_prev: int, mul_cur: int,
+                     error_flag: torch.Tensor) -> None:
+    """``residual[t] = table[ids[t]] + bigram[(before * mul_prev + ids[t] * mul_cur) mod buckets]`` in
+    float32, ``before`` being the token ahead of t in its request: the one in this step, or, for a
+    portion's first token, ``previous[slot]``; a sequence's first token takes the table's last row.
+    ``previous`` (int32 ``[slots + 1, 1]``) then holds every request's last token."""
+    vocab, hidden = table.shape
+    tokens = ids.shape[0]
+    buckets = bigram.shape[0] - 1
+    requests = slots.shape[0]
+    _run("norm_ext", "b200_bigram_embedding",
+         _P(_check("embedding table", table, _RUN)), _P(_check("bigram table", bigram, table.dtype, (buckets + 1, hidden))),
+         _P(_check("token ids", ids, torch.int32, (tokens,))), _P(_check("positions", positions, torch.int32, (tokens,))),
+         _P(_check("request of each token", token_request, torch.int32, (tokens,))),
+         _P(_check("query_start", query_start, torch.int32, (requests + 1,))),
+         _P(_check("state slots", slots, torch.int32, (requests,))),
+         _P(_check("previous tokens", previous, torch.int32)),
+         _P(_check("residual", residual, torch.float32, (tokens, hidden))),
+         _I(tokens), _I(hidden), _I(vocab), _I(buckets), _I(mul_prev), _I(mul_cur),
+         _P(_check("error flag", error_flag, torch.int32)), _I(_code(table.dtype)), _stream())
+
+
+# -------------------------------------------------------------------- attention
+def head_norm_scale_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                          q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
+                          temperature: tuple[float, int] | None, q_out: torch.Tensor,
+                          k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, num_q_heads: int,
+                          num_kv_heads: int, head_dim: int, value_dim: int, page_size: int) -> None:
+    """From the packed projection ``[T, nq d + nkv d + nkv dv]``: per-head RMSNorm of queries and
+    keys, queries times ``1 + coef * ln(floor((p + 1) / every) + 1)`` for ``temperature = (coef,
+    every)``, queries to ``q_out``, keys and values to their pages at ``slots``."""
+    tokens = qkv.shape[0]
+    dtype = qkv.dtype
+    width = (num_q_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim
+    coef, every = temperature if temperature is not None else (0.0, 0)
+    _run("attention_bias", "b200_head_norm_scale_cache",
+         _P(_check("qkv", qkv, _RUN, (tokens, width))),
+         _P(_check("positions", positions, torch.int32, (tokens,))),
+         _P(_check("slot mapping", slots, torch.int32, (tokens,))),
+         _P(_check("q head-norm weight", q_weight, torch.float32, (head_dim,), optional=True)),
+         _P(_check("k head-norm weight", k_weight, torch.float32, (head_dim,), optional=True)),
+         _P(_check("q output", q_out, dtype, (tokens, num_q_heads * head_dim))),
+         _P(_check("key pages", k_pages, dtype, (None, num_kv_heads, page_size, head_dim), optional=True)),
+         _P(_check("value pages", v_pages, dtype, (None, num_kv_heads, page_size, value_dim), optional=True)),
+         _I(tokens), _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(value_dim), _I(page_size),
+         _F(eps), _F(coef), _I(every), _I(_code(dtype)), _stream())
+
+
+def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                           query_start: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
+                           slopes: torch.Tensor | None, num_q_heads: int, num_kv_heads: int, head_dim: int,
+                           value_dim: int, page_size: int, scale: float, window: int | None) -> None:
+    """Causal attention of every request's new queries over its pages with the score ``q . k * scale
+    - slopes[h] * (i - j)``; scores, weights and the weighted sum in float32."""
+    tokens = q.shape[0]
+    requests = seq_lens.shape[0]
+    dtype = q.dtype
+    _run("attention_bias", "b200_biased_paged_attention",
+         _P(_check("queries", q, _RUN, (tokens, num_q_heads * head_dim))),
+         _P(_check("key pages", k_pages, dtype, (None, num_kv_heads, page_size, head_dim))),
+         _P(_check("value pages", v_pages, dtype, (None, num_kv_heads, page_size, value_dim))),
+         _P(_check("attention output", out, dtype, (tokens, num_q_heads * value_dim))),
+         _P(_check("query_start", query_start, torch.int32, (requests + 1,))),
+         _P(_check("seq_lens", seq_lens, torch.int32, (requests,))),
+         _P(_check("block table", block_table, torch.int32, (requests, None))),
+         _P(_check("slopes", slopes, torch.float32, (num_q_heads,), optional=True)),
+         _I(requests), _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
+         _I(value_dim), _I(page_size), _F(scale), _I(window or 0), _I(_code(dtype)), _stream())
+
+
+# ------------------------------------------------------------------ recurrences
+def decayed_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], decay: torch.Tensor,
+                             query_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
+                             y: torch.Tensor, heads: int, key_dim: int, value_dim: int) -> None:
+    """Per request and head, token after token: ``S <- decay_h S + k v^T``, ``y = S^T q`` with q, k
+    (``heads x key_dim``) and v (``heads x value_dim``) = silu of the columns of ``proj`` that start
+    at ``offsets = (q, k, v)``.  ``state``: float32 ``[slots + 1, heads, key_dim, value_dim]``, read
+    at the request's slot and left advanced; ``y``: float32 ``[T, heads * value_dim]``."""
+    tokens, stride = proj.shape
+    requests = slots.shape[0]
+    _run("recurrence", "b200_decayed_linear_attention",
+         _P(_check("projection", proj, _RUN)), _I(stride), _I(offsets[0]), _I(offsets[1]), _I(offsets[2]),
+         _P(_check("decay", decay, torch.float32, (heads,))),
+         _P(_check("query_start", query_start, torch.int32, (requests + 1,))),
+         _P(_check("state slots", slots, torch.int32, (requests,))),
+         _P(_check("state", state, torch.float32, (None, heads, key_dim, value_dim))),
+         _P(_check("recurrence output", y, torch.float32, (tokens, heads * value_dim))),
+         _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(_code(proj.dtype)), _stream())
+
+
+def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bias: torch.Tensor,
+                   a_log: torch.Tensor, skip: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
+                   state: torch.Tensor, y: torch.Tensor, heads: int, groups: int, state_dim: int,
+                   value_dim: int) -> None:
+    """Per request and head, token after token, with ``dt = softplus(proj[t, dt_offset + h] +
+    dt_bias[h])``: ``S <- exp(-exp(a_log_h) dt) S + dt B x^T``, ``y = S^T C + skip_h x``; x, B and C are
+    the columns ``[heads * value_dim | groups * state_dim | groups * state_dim]`` of the float32
+    ``xbc``.  ``state``: float32 ``[slots + 1, heads, state_dim, value_dim]``."""
+    tokens = xbc.shape[0]
+    requests = slots.shape[0]
+    width = heads * value_dim + 2 * groups * state_dim
+    _run("recurrence", "b200_selective_scan",
+         _P(_check("convolved inputs", xbc, torch.float32, (tokens, width))), _I(width),
+         _P(_check("projection", proj, _RUN, (tokens, None))), _I(proj.shape[1]), _I(dt_offset),
+         _P(_check("dt bias", dt_bias, torch.float32, (heads,))), _P(_check("A_log", a_log, torch.float32, (heads,))),
+         _P(_check("skip", skip, torch.float32, (heads,))),
+         _P(_check("query_start", query_start, torch.int32, (requests + 1,))),
+         _P(_check("state slots", slots, torch.int32, (requests,))),
+         _P(_check("state", state, torch.float32, (None, heads, state_dim, value_dim))),
+         _P(_check("recurrence output", y, torch.float32, (tokens, heads * value_dim))),
+         _I(requests), _I(heads), _I(groups), _I(state_dim), _I(value_dim), _I(_code(proj.dtype)), _stream())
+
+
+def causal_conv_silu(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor,
+                     state: torch.Tensor, token_request: torch.Tensor, query_start: torch.Tensor,
+                     slots: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t, c] = silu(bias[c] + sum_i weight[c, i] * in[t - (taps - 1 - i), c])`` over the columns
+    ``offset .. offset + channels`` of ``proj``, within each request; what lies before a step's
+    portion comes from ``state`` (float32 ``[slots + 1, taps - 1, channels]``: the request's last
+    inputs, oldest first), which then receives the last inputs of this step."""
+    tokens = proj.shape[0]
+    channels, taps = weight.shape
+    requests = slots.shape[0]
+    _run("recurrence", "b200_causal_conv_silu",
+         _P(_check("projection", proj, _RUN, (tokens, None))), _I(proj.shape[1]), _I(offset),
+         _P(_check("conv weight", weight, torch.float32)), _P(_check("conv bias", bias, torch.float32, (channels,))),
+         _P(_check("conv state", state, torch.float32, (None, taps - 1, channels))),
+         _P(_check("request of each token", token_request, torch.int32, (tokens,))),
+         _P(_check("query_start", query_start, torch.int32, (requests + 1,))),
+         _P(_check("state slots", slots, torch.int32, (requests,))),
+         _P(_check("convolved output", out, torch.float32, (tokens, channels))),
+         _I(tokens), _I(requests), _I(channels), _I(taps), _I(_code(proj.dtype)), _stream())
+    if taps > 1:
+        count_launch()          # the kernel that replaces the state

@@ -124,3 +124,98 @@ class PagedAttention(Mixer):
         squares = torch.empty((tokens, self.env.hidden_size // 8), dtype=torch.float32, device=x.device)
         kernels.gemm(attended, self.out_proj, out, fold=(residual, weight, squares))
         return HalfNormedRows(out, squares, eps)
+
+
+def power_of_two_slopes(num_heads: int, span: float = 8.0) -> list[float]:
+    """``2 ** (-span * (h + 1) / num_heads)`` for head h: the slopes of a linear distance bias."""
+    return [2.0 ** (-span * (head + 1) / num_heads) for head in range(num_heads)]
+
+
+@MIXERS.register("biased_attention")
+class BiasedAttention(Mixer):
+    """Causal softmax attention over a paged cache in which positions enter as a bias on the
+    scores, not as a rotation: ``score(i, j) = q_i . k_j * scale - slope_h * (i - j)``.  Grouped
+    key/value heads; keys and values may have sizes of their own; optional per-head RMSNorm of
+    queries and keys (one plain weight vector for all heads); optional query temperature ``1 + coef
+    * ln(floor((p + 1) / every) + 1)`` at position p.  Scores, softmax weights and the weighted sum
+    are float32 in both run modes.
+
+    params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``value_dim`` (default ``head_dim``),
+    ``scale``, ``slopes`` (one per head, or None for no bias), ``window`` (None = all keys),
+    ``qk_norm_eps`` (None = no head norm), ``q_temperature`` (``(coef, every)`` or None),
+    ``weight_names`` (q, k, v, o matrices, q and k norm vectors)."""
+
+    graph_safe = True
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv, position: PositionEncoding) -> None:
+        super().__init__(params, env, position)
+        if position.rotary_dim:
+            raise ValueError("biased attention takes no rotation: give it position encoding 'none'")
+        self.num_heads = int(params["num_heads"])
+        self.num_kv_heads = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.value_dim = int(params.get("value_dim") or self.head_dim)
+        self.scale = float(params.get("scale", self.head_dim ** -0.5))
+        window = params.get("window")
+        self.window = None if window is None else int(window)
+        eps = params.get("qk_norm_eps")
+        self.qk_norm_eps = None if eps is None else float(eps)
+        temperature = params.get("q_temperature")
+        self.q_temperature = None if temperature is None else (float(temperature[0]), int(temperature[1]))
+        slopes = params.get("slopes")
+        self.slopes_host = None if slopes is None else [float(s) for s in slopes]
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"num_heads={self.num_heads} is not a multiple of num_kv_heads={self.num_kv_heads}")
+        if self.head_dim > 512 or self.value_dim > 512:
+            raise ValueError(f"head_dim={self.head_dim}, value_dim={self.value_dim}: sizes up to 512 are built")
+        if self.slopes_host is not None and len(self.slopes_host) != self.num_heads:
+            raise ValueError(f"{len(self.slopes_host)} slopes for {self.num_heads} heads")
+        if self.q_temperature is not None and self.q_temperature[1] <= 0:
+            raise ValueError(f"q_temperature every={self.q_temperature[1]} must be positive")
+        self.names = tuple(params.get("weight_names", ("q_proj.weight", "k_proj.weight", "v_proj.weight",
+                                                       "o_proj.weight", "q_norm.weight", "k_norm.weight")))
+        self.slopes = (None if self.slopes_host is None
+                       else torch.tensor(self.slopes_host, dtype=torch.float64).to(torch.float32).to(env.device))
+        self.qkv = self.out_proj = self.q_norm = self.k_norm = None
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        hidden, d, dv = self.env.hidden_size, self.head_dim, self.value_dim
+        q, k, v, o, qn, kn = self.names
+        names = {q: WeightInfo((self.num_heads * d, hidden)), k: WeightInfo((self.num_kv_heads * d, hidden)),
+                 v: WeightInfo((self.num_kv_heads * dv, hidden)), o: WeightInfo((hidden, self.num_heads * dv))}
+        if self.qk_norm_eps is not None:
+            names[qn] = WeightInfo((d,), "vector")
+            names[kn] = WeightInfo((d,), "vector")
+        return names
+
+    def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        q, k, v, o, qn, kn = self.names
+        self.qkv = torch.cat([tensors[q], tensors[k], tensors[v]], dim=0).contiguous()
+        self.out_proj = tensors[o].contiguous()
+        if self.qk_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors[qn], tensors[kn]
+
+    def cache_need(self) -> KVPagesNeed:
+        return KVPagesNeed(self.num_kv_heads, self.head_dim, self.window, self.value_dim)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        if cache.kind != "pages":
+            raise ValueError("biased attention needs a cache of pages")
+        group = ctx.groups[cache.group]
+        tokens = x.shape[0]
+        nq, nkv, d, dv = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        qkv = torch.empty((tokens, self.qkv.shape[0]), dtype=x.dtype, device=x.device)
+        kernels.gemm(x, self.qkv, qkv)
+        q = torch.empty((tokens, nq * d), dtype=x.dtype, device=x.device)
+        store = cache.writable
+        kernels.head_norm_scale_cache(
+            qkv, ctx.positions, group.slot_mapping, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0,
+            self.q_temperature, q, cache.keys if store else None, cache.values if store else None, nq, nkv, d, dv,
+            group.page_size)
+        attended = torch.empty((tokens, nq * dv), dtype=x.dtype, device=x.device)
+        kernels.biased_paged_attention(
+            q, cache.keys, cache.values, attended, ctx.query_start, ctx.seq_lens, group.block_table, self.slopes,
+            nq, nkv, d, dv, group.page_size, self.scale, self.window)
+        out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
+        kernels.gemm(attended, self.out_proj, out)
+        return out

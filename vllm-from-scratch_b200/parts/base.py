@@ -47,14 +47,19 @@ class KVPagesNeed:
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    # Size of a value head where it differs from the keys' (None: the same).  Keys and values
+    # then live in slabs of their own.
+    value_dim: int | None = None
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A tensor of fixed shape per request, addressed by the request's slot."""
+    """A tensor of fixed shape per request, addressed by the request's slot.  A part that
+    needs several names each (``CacheView.states[name]``)."""
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+    name: str = "state"
 
 
 # ---------------------------------------------------------------- step context
@@ -99,6 +104,9 @@ class CacheView:
     ``kind`` is "pages" (``keys``/``values`` are ``[pages, kv_heads, page_size,
     head_dim]`` views of this entry's slab and ``group`` indexes
     ``StepContext.groups``), "state" (``state`` is ``[slots, *shape]``) or "none".
+    A part that asked for several things (``cache_need`` returned a tuple: at most one
+    :class:`KVPagesNeed` and any number of :class:`StateNeed`) finds its pages as above and
+    every state tensor under its name in ``states``; ``state`` is the first of them.
     ``writable`` is False when the cache belongs to another schedule entry.
     """
 
@@ -108,6 +116,19 @@ class CacheView:
     values: torch.Tensor | None = None
     state: torch.Tensor | None = None
     writable: bool = True
+    states: dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+@dataclass
+class NormedAddend:
+    """Rows that are still to be normalised on their way into the residual stream:
+    ``residual += rows * rsqrt(mean(rows**2) + eps) * weight``.  A block with a norm behind a
+    sublayer hands this to the next norm in place of plain rows, and the two norms and the sum
+    between them run as one kernel."""
+
+    rows: torch.Tensor
+    weight: torch.Tensor
+    eps: float
 
 
 @dataclass
@@ -178,7 +199,9 @@ class Mixer(Part):
         super().__init__(params, env)
         self.position = position
 
-    def cache_need(self) -> KVPagesNeed | StateNeed | None:
+    def cache_need(self) -> KVPagesNeed | StateNeed | tuple | None:
+        """What one execution of the mixer owns: pages, a state tensor, or a tuple of at most
+        one :class:`KVPagesNeed` and any number of :class:`StateNeed` with names of their own."""
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
@@ -207,6 +230,11 @@ class Embedding(Part):
     """From token ids to the first content of the float32 residual stream.  params always
     hold ``vocab_size``.  ``table()`` is the ``[vocab, hidden]`` matrix an output head that
     is tied to the embedding multiplies by."""
+
+    def cache_need(self) -> StateNeed | tuple | None:
+        """State per request that the embedding keeps from step to step (an earlier token, for
+        instance); ``forward`` is then called with ``cache=`` a "state" :class:`CacheView`."""
+        return None
 
     def forward(self, token_ids: torch.Tensor, ctx: StepContext, residual: torch.Tensor,
                 error_flag: torch.Tensor) -> None:

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import BLOCKS, Block, CacheView, HalfNormedRows, Norm, StepContext
+from .base import BLOCKS, Block, CacheView, HalfNormedRows, Norm, StepContext  # noqa: F401
 
 
 @BLOCKS.register("pre_norm")
@@ -44,3 +44,33 @@ class PreNormBlock(Block):
             return self.feed_forward.forward(normed, ctx)
         half = self.mixer.forward(normed, ctx, cache, fold=(residual, self.norms["feed_forward"]))
         return self.feed_forward.forward(half, ctx, fold=None if next_norm is None else (residual, next_norm))
+
+
+@BLOCKS.register("sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm in front of and behind each sublayer: ``h += post_mixer(mixer(mixer_norm(h)))``, then,
+    where the layer has a feed-forward, ``h += post_feed_forward(feed_forward(feed_forward_norm(h)))``.
+
+    What a sublayer returns travels on as a :class:`~.base.NormedAddend` under the norm behind it, so
+    that norm, the sum into the residual and the norm in front of the next sublayer (the next layer's,
+    or the model's last one) are one kernel."""
+
+    graph_safe = True
+    needs_feed_forward = False
+
+    def __init__(self, params, env, *, mixer, feed_forward, norms) -> None:
+        self.norm_roles = (("mixer", "post_mixer", "feed_forward", "post_feed_forward") if feed_forward is not None
+                           else ("mixer", "post_mixer"))
+        super().__init__(params, env, mixer=mixer, feed_forward=feed_forward, norms=norms)
+        for role, norm in self.norms.items():
+            if role.startswith("post_") and not hasattr(norm, "addend"):
+                raise ValueError(f"block at {env.prefix!r}: the norm behind a sublayer ({role}) must be able to "
+                                 f"travel with its rows (an `addend` method)")
+
+    def forward(self, x, residual: torch.Tensor, ctx: StepContext, cache: CacheView):
+        normed = self.norms["mixer"].forward(x, residual)
+        mixed = self.norms["post_mixer"].addend(self.mixer.forward(normed, ctx, cache))
+        if self.feed_forward is None:
+            return mixed
+        normed = self.norms["feed_forward"].forward(mixed, residual)
+        return self.norms["post_feed_forward"].addend(self.feed_forward.forward(normed, ctx))

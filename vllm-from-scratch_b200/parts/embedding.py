@@ -15,7 +15,8 @@ from typing import Any, Mapping
 import torch
 
 from .. import kernels
-from .base import EMBEDDINGS, OUTPUT_HEADS, Embedding, OutputHead, PartEnv, StepContext, WeightInfo
+from .base import (EMBEDDINGS, OUTPUT_HEADS, CacheView, Embedding, OutputHead, PartEnv, StateNeed, StepContext,
+                   WeightInfo)
 
 
 @EMBEDDINGS.register("token_embedding")
@@ -43,9 +44,58 @@ class TokenEmbedding(Embedding):
         return self.weight
 
 
+@EMBEDDINGS.register("bigram_embedding")
+class BigramEmbedding(Embedding):
+    """A row per token plus a row per pair (previous token, token) from a hashed table: row
+    ``(previous * mul_prev + token * mul_cur) mod buckets`` of ``bigram`` (``buckets + 1`` rows; the
+    last one is for a sequence's first token).  The previous token is state of the request: the
+    kernel reads it from the request's slot for the first token of a portion and leaves the
+    portion's last token there.
+
+    params: ``vocab_size``, ``buckets``, ``mul_prev``, ``mul_cur``; ``weight_names`` (token table,
+    bigram table; default ``weight``, ``bigram``)."""
+
+    graph_safe = True
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
+        super().__init__(params, env)
+        self.vocab_size = int(params["vocab_size"])
+        self.buckets = int(params["buckets"])
+        self.mul_prev, self.mul_cur = int(params["mul_prev"]), int(params["mul_cur"])
+        if self.buckets <= 0:
+            raise ValueError(f"bigram embedding: buckets={self.buckets}")
+        self.names = tuple(params.get("weight_names", ("weight", "bigram")))
+        self.weight: torch.Tensor | None = None
+        self.bigram: torch.Tensor | None = None
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        hidden = self.env.hidden_size
+        return {self.names[0]: WeightInfo((self.vocab_size, hidden)),
+                self.names[1]: WeightInfo((self.buckets + 1, hidden))}
+
+    def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.names[0]].contiguous()
+        self.bigram = tensors[self.names[1]].contiguous()
+
+    def cache_need(self) -> StateNeed:
+        return StateNeed((1,), torch.int32, name="previous_token")
+
+    def forward(self, token_ids: torch.Tensor, ctx: StepContext, residual: torch.Tensor,
+                error_flag: torch.Tensor, cache: CacheView | None = None) -> None:
+        if cache is None or cache.state is None:
+            raise ValueError("the bigram embedding keeps the previous token per request: it needs its state")
+        kernels.bigram_embedding(self.weight, self.bigram, token_ids, ctx.positions, ctx.token_request,
+                                 ctx.query_start, ctx.state_slots, cache.state, residual, self.mul_prev,
+                                 self.mul_cur, error_flag)
+
+    def table(self) -> torch.Tensor:
+        return self.weight
+
+
 @OUTPUT_HEADS.register("linear_head")
 class LinearHead(OutputHead):
-    """params: ``vocab_size``, ``tied`` (default False)."""
+    """params: ``vocab_size``, ``tied`` (default False), ``scale`` (the logits are multiplied by it;
+    default 1), ``weight_name`` (default ``weight``; empty: the prefix itself is the tensor)."""
 
     graph_safe = True
 
@@ -53,13 +103,15 @@ class LinearHead(OutputHead):
         super().__init__(params, env)
         self.vocab_size = int(params["vocab_size"])
         self.tied = bool(params.get("tied", False))
+        self.scale = float(params.get("scale", 1.0))
+        self.weight_name = str(params.get("weight_name", "weight"))
         self.weight: torch.Tensor | None = None
 
     def expected_weights(self) -> dict[str, WeightInfo]:
-        return {} if self.tied else {"weight": WeightInfo((self.vocab_size, self.env.hidden_size))}
+        return {} if self.tied else {self.weight_name: WeightInfo((self.vocab_size, self.env.hidden_size))}
 
     def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.weight_name].contiguous()
 
     def bind_embedding(self, embedding: Embedding) -> None:
         if self.tied:
@@ -68,4 +120,6 @@ class LinearHead(OutputHead):
     def forward(self, normed: torch.Tensor) -> torch.Tensor:
         out = torch.empty((normed.shape[0], self.vocab_size), dtype=torch.float32, device=normed.device)
         kernels.gemm(normed, self.weight, out)
+        if self.scale != 1.0:
+            out.mul_(self.scale)        # float32, one rounding per logit
         return out

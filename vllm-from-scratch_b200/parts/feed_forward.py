@@ -15,27 +15,28 @@ from .base import FEED_FORWARDS, FeedForward, HalfNormedRows, Norm, PartEnv, Ste
 
 @FEED_FORWARDS.register("gated_silu")
 class GatedSiluFeedForward(FeedForward):
-    """params: ``intermediate_size``."""
+    """params: ``intermediate_size``; ``weight_names`` (the checkpoint's names of the gate, up and
+    down matrices under the part's prefix; default ``gate_proj.weight``, ``up_proj.weight``,
+    ``down_proj.weight``)."""
 
     graph_safe = True
 
     def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
         super().__init__(params, env)
         self.intermediate_size = int(params["intermediate_size"])
+        self.names = tuple(params.get("weight_names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
         self.gate_up: torch.Tensor | None = None
         self.down: torch.Tensor | None = None
 
     def expected_weights(self) -> dict[str, WeightInfo]:
         inter, hidden = self.intermediate_size, self.env.hidden_size
-        return {
-            "gate_proj.weight": WeightInfo((inter, hidden)),
-            "up_proj.weight": WeightInfo((inter, hidden)),
-            "down_proj.weight": WeightInfo((hidden, inter)),
-        }
+        gate, up, down = self.names
+        return {gate: WeightInfo((inter, hidden)), up: WeightInfo((inter, hidden)), down: WeightInfo((hidden, inter))}
 
     def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
-        self.down = tensors["down_proj.weight"].contiguous()
+        gate, up, down = self.names
+        self.gate_up = torch.cat([tensors[gate], tensors[up]], dim=0).contiguous()
+        self.down = tensors[down].contiguous()
 
     def splits_norms(self, tokens: int) -> bool:
         return (kernels.split_norm_ok(tokens, self.gate_up, fold=False, gated=True)

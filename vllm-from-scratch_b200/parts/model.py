@@ -108,23 +108,31 @@ class DecoderModel:
         return total
 
     # ------------------------------------------------------------------- cache
-    def cache_needs(self) -> list[KVPagesNeed | StateNeed | None]:
+    def cache_needs(self) -> list:
         """One entry per schedule entry: what its execution must own (None when
         it owns nothing, including when it reads another entry's cache)."""
-        needs: list[KVPagesNeed | StateNeed | None] = []
+        needs: list = []
         for entry in self.spec.schedule:
             need = self.layers[entry.layer].mixer.cache_need()
             needs.append(None if entry.cache_from is not None else need)
         return needs
 
     # ----------------------------------------------------------------- forward
-    def forward(self, token_ids: torch.Tensor, ctx: StepContext, caches: list[CacheView]
+    def forward(self, token_ids: torch.Tensor, ctx: StepContext, caches: list[CacheView],
+                embedding_cache: CacheView | None = None, trail: list | None = None
                 ) -> tuple[torch.Tensor | None, torch.Tensor]:
         """Run every schedule entry over the batch.  Returns the last layer's
-        not-yet-added output and the float32 residual stream."""
+        not-yet-added output and the float32 residual stream.  ``embedding_cache``: the state
+        of an embedding that keeps some (``Embedding.cache_need``).  ``trail``: a list that
+        receives ``(x, residual copy)`` after every layer execution, for looking inside."""
         tokens = token_ids.shape[0]
         residual = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=token_ids.device)
-        self.embedding.forward(token_ids, ctx, residual, self._token_error)
+        if embedding_cache is not None:
+            self.embedding.forward(token_ids, ctx, residual, self._token_error, cache=embedding_cache)
+        else:
+            if self.embedding.cache_need() is not None:
+                raise ValueError("the embedding keeps state per request: hand its cache over (embedding_cache=)")
+            self.embedding.forward(token_ids, ctx, residual, self._token_error)
         x = None
         blocks = [self.layers[entry.layer] for entry in self.spec.schedule]
         for number, (block, cache) in enumerate(zip(blocks, caches)):
@@ -137,6 +145,8 @@ class DecoderModel:
                 x = block.forward(x, residual, ctx, cache, next_norm=norm)
             else:
                 x = block.forward(x, residual, ctx, cache)
+            if trail is not None:
+                trail.append((x, residual.clone()))
         return x, residual
 
     def logits(self, x: torch.Tensor | None, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

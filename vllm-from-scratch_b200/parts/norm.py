@@ -12,12 +12,18 @@ from typing import Any, Mapping
 import torch
 
 from .. import kernels
-from .base import NORMS, Norm, PartEnv, WeightInfo
+from .base import NORMS, Norm, NormedAddend, PartEnv, WeightInfo
 
 
 @NORMS.register("rms_norm")
 class RMSNorm(Norm):
-    """params: ``eps`` (inside the root), ``size`` (defaults to the residual width)."""
+    """params: ``eps`` (inside the root), ``size`` (defaults to the residual width), ``offset``
+    (default 0: the checkpoint's vector is the weight; 1 for a vector stored around zero, the weight
+    being ``1 + w``), ``weight_name`` (the tensor's name under the part's prefix, default ``weight``;
+    empty: the prefix itself is the tensor).
+
+    ``forward`` also takes a :class:`~.base.NormedAddend` for ``x``: rows that pass through a norm of
+    their own on their way into the residual; both norms and the sum are then one kernel."""
 
     graph_safe = True
 
@@ -25,21 +31,32 @@ class RMSNorm(Norm):
         super().__init__(params, env)
         self.eps = float(params["eps"])
         self.size = int(params.get("size", env.hidden_size))
+        self.offset = float(params.get("offset", 0.0))
+        self.weight_name = str(params.get("weight_name", "weight"))
         self.weight: torch.Tensor | None = None
 
     def expected_weights(self) -> dict[str, WeightInfo]:
-        return {"weight": WeightInfo((self.size,), "vector")}
+        return {self.weight_name: WeightInfo((self.size,), "vector")}
 
     def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()      # float32: formed once, as the norm would
+
+    def addend(self, rows: torch.Tensor) -> NormedAddend:
+        """``rows`` on their way into the residual through this norm."""
+        return NormedAddend(rows, self.weight, self.eps)
 
     def split(self) -> tuple[torch.Tensor, float] | None:
         return (self.weight, self.eps) if self.size == self.env.hidden_size else None
 
-    def forward(self, x: torch.Tensor | None, residual: torch.Tensor, out: torch.Tensor | None = None,
+    def forward(self, x: torch.Tensor | NormedAddend | None, residual: torch.Tensor, out: torch.Tensor | None = None,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
         if out is None:
             count = residual.shape[0] if rows is None else rows.shape[0]
             out = torch.empty((count, self.size), dtype=self.env.dtype, device=residual.device)
-        kernels.add_rmsnorm(x, residual, self.weight, self.eps, out, rows)
+        if isinstance(x, NormedAddend):
+            kernels.add_normed_rmsnorm(x.rows, x.weight, x.eps, residual, self.weight, self.eps, out, rows)
+        else:
+            kernels.add_rmsnorm(x, residual, self.weight, self.eps, out, rows)
         return out

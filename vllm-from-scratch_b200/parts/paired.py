@@ -1,0 +1,101 @@
+"""Two mixers side by side on the same input: ``(rms(left(h)) * w_left + rms(right(h)) * w_right) / 2``,
+each branch's output normalised over the model width with a plain weight vector of its own before the
+mean.  The branches are mixers of any registered kind, built from their own :class:`~.spec.PartSpec`;
+their tensors live under the names the specs give (``left`` and ``right`` by default), their cache
+needs are handed on together (at most one of them may keep pages), and each finds its share of the
+layer's :class:`~.base.CacheView`.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Mapping
+
+import torch
+
+from .. import kernels
+from .base import (MIXERS, CacheView, KVPagesNeed, Mixer, PartEnv, PositionEncoding, StateNeed, StepContext,
+                   WeightInfo)
+from .spec import PartSpec
+
+
+def _join(prefix: str, name: str) -> str:
+    return f"{prefix}.{name}" if prefix and name else prefix or name
+
+
+@MIXERS.register("paired_mixers")
+class PairedMixers(Mixer):
+    """params: ``branches`` (two :class:`~.spec.PartSpec` of mixers; each spec's ``name`` is the segment
+    of its tensors and of its output norm vector ``<name>.<out_name>``), ``eps``, ``out_name`` (default
+    ``out``)."""
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv, position: PositionEncoding) -> None:
+        super().__init__(params, env, position)
+        branches = tuple(params["branches"])
+        if len(branches) != 2 or not all(isinstance(branch, PartSpec) for branch in branches):
+            raise ValueError("paired mixers take two branches, each the spec of a mixer")
+        if not all(branch.name for branch in branches) or branches[0].name == branches[1].name:
+            raise ValueError("the two branches need names of their own")
+        self.eps = float(params["eps"])
+        self.out_name = str(params.get("out_name", "out"))
+        self.specs = branches
+        self.branches: list[Mixer] = [
+            MIXERS.get(branch.kind)(branch.params, PartEnv(env.hidden_size, env.dtype, env.device,
+                                                           _join(env.prefix, branch.name)), position)
+            for branch in branches]
+        self.out_weights: list[torch.Tensor | None] = [None, None]
+
+    @property
+    def graph_safe(self) -> bool:       # a pair may be replayed if both branches may
+        return all(branch.graph_safe for branch in self.branches)
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        names: dict[str, WeightInfo] = {}
+        for spec, branch in zip(self.specs, self.branches):
+            for name, info in branch.expected_weights().items():
+                names[_join(spec.name, name)] = info
+            names[_join(spec.name, self.out_name)] = WeightInfo((self.env.hidden_size,), "vector")
+        return names
+
+    def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for index, (spec, branch) in enumerate(zip(self.specs, self.branches)):
+            branch.load_weights({name: tensors[_join(spec.name, name)] for name in branch.expected_weights()})
+            self.out_weights[index] = tensors[_join(spec.name, self.out_name)]
+
+    # -------------------------------------------------------------------- cache
+    def _needs(self) -> list[list]:
+        found = []
+        for branch in self.branches:
+            need = branch.cache_need()
+            found.append([] if need is None else list(need) if isinstance(need, (tuple, list)) else [need])
+        return found
+
+    def cache_need(self) -> tuple | None:
+        merged: list = []
+        for spec, needs in zip(self.specs, self._needs()):
+            for need in needs:
+                if isinstance(need, StateNeed):
+                    need = StateNeed(need.shape, need.dtype, name=_join(spec.name, need.name))
+                merged.append(need)
+        if sum(isinstance(need, KVPagesNeed) for need in merged) > 1:
+            raise ValueError("only one of two paired mixers may keep pages of keys and values")
+        return tuple(merged) or None
+
+    def _view(self, index: int, cache: CacheView) -> CacheView:
+        """The branch's share of the layer's cache, under the names the branch gave."""
+        needs = self._needs()[index]
+        prefix = self.specs[index].name + "."
+        states = {name[len(prefix):]: tensor for name, tensor in cache.states.items() if name.startswith(prefix)}
+        first = next(iter(states.values()), None)
+        if any(isinstance(need, KVPagesNeed) for need in needs):
+            return CacheView("pages", cache.group, cache.keys, cache.values, first, cache.writable, states)
+        if states:
+            return CacheView("state", state=first, writable=cache.writable, states=states)
+        return CacheView("none")
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        left = self.branches[0].forward(x, ctx, self._view(0, cache))
+        right = self.branches[1].forward(x, ctx, self._view(1, cache))
+        out = torch.empty_like(left)
+        kernels.paired_norm_mean(left, self.out_weights[0], right, self.out_weights[1], self.eps, out)
+        return out
