@@ -147,8 +147,10 @@ def fill_cache_randomly(runner) -> None:
     """Keys and values of the whole pool drawn at random (scaled like normalised keys): what a
     decode step reads is then as real as what a prefill would have left, without running one."""
     for group in runner.storage.groups:
-        for layer in range(group.slab.shape[0]):
-            group.slab[layer].normal_(0.0, 1.0)
+        for slab in (group.slab, group.value_slab):
+            if slab is not None:
+                for layer in range(slab.shape[0]):
+                    slab[layer].normal_(0.0, 1.0)
 
 
 def hold_context(runner, request_id: str, tokens: int) -> None:
@@ -528,6 +530,101 @@ def run_mixed(args, measured, peak_kind) -> dict:
     }
 
 
+# ------------------------------------------------------------------- two designs side by side
+def _bemuzen(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> dict:
+    """Layers of the sizes of a Qwen3 layer of this width: the softmax branch has the Qwen3 layer's
+    heads, the linear branch half as many of the same sizes, the selective scan twice the width in
+    heads of 64 with 128 rows of state; every fourth layer (the second first) is a selective scan."""
+    parallel = {"type": "parallel", "mlp": {"kind": "dense", "ff": inter}, "mixer": {
+        "left": {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "q_temp": {"coef": 0.1, "every": 1024}},
+        "right": {"heads": heads // 2, "dim": 128, "vdim": 128,
+                  "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, heads // 2 - 1)) for h in range(heads // 2)]}}}
+    scan = {"type": "mamba2", "mlp": {"kind": "dense", "ff": inter}, "mixer": {
+        "heads": 2 * hidden // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    return {"architecture": "Bemuzen", "vocab": vocab, "width": hidden, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "layers": [scan if index % 4 == 1 else parallel for index in range(layers)]}
+
+
+DESIGN_SIZES = {      # name -> (hidden, heads, feed-forward width)
+    "1.7b-layers": (2048, 16, 6144),
+    "8b-layers": (4096, 32, 12288),
+}
+
+
+def measure_prompt_steps(runner, config, tokens: int) -> dict:
+    """One prompt of ``tokens`` tokens in one step through the step function (no graph: models that
+    keep state per request run their prompt steps that way in the engine), one row of logits; the
+    median per step over at least three regions of at least 200 ms, by CUDA events."""
+    import torch
+    from vllm_from_scratch_b200 import StepEntry
+    counter = [0]
+
+    def one_step() -> None:
+        request_id = f"prompt-{counter[0]}"
+        prompt = random_prompt(config.vocab_size, tokens, seed=7000 + counter[0] % 7)
+        counter[0] += 1
+        runner.manager.admit(request_id)
+        assert runner.manager.allocate(request_id, tokens)
+        runner.step([StepEntry(request_id, prompt, 0, [tokens - 1])])
+        runner.manager.release(request_id)
+
+    def region(count: int) -> float:
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(count):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / count
+
+    for _ in range(3):
+        one_step()
+    estimate = region(3)
+    count = max(3, math.ceil(MIN_REGION_MS / estimate))
+    times = [region(count) for _ in range(MIN_REPEATS)]
+    ms = statistics.median(times)
+    return {"ms": round(ms, 3), "tok_s": round(tokens * 1000.0 / ms, 1), "steps_timed": count, "spread": spread(times)}
+
+
+def run_design(args, measured, peak_kind) -> dict:
+    """``--design bemuzen``: prompt steps and decode steps of Bemuzen layers beside Qwen3 layers of the
+    same width, heads, feed-forward, number of layers and vocabulary (random weights, bfloat16)."""
+    import torch
+    layers, vocab, context = args.layers or 4, 32768, args.context or 4096
+    points = {}
+    with ClockSampler() as clocks:
+        for name, (hidden, heads, inter) in DESIGN_SIZES.items():
+            qwen = dict(_qwen3(layers, hidden, heads, inter, False), vocab_size=vocab)
+            for label, raw in (("bemuzen", _bemuzen(layers, hidden, heads, inter, vocab)), ("qwen3", qwen)):
+                most = max(64 * (args.prompt_len + 600 + args.block_size), 8192 + 64)
+                runner, config = build_runner(raw, 64, most, args.block_size)
+                fill_cache_randomly(runner)
+                entry = {"parameters_m": round(runner.model.num_weight_bytes() / 2e6, 1)}
+                for tokens in (2048, 8192):
+                    entry[f"prefill_{tokens}"] = measure_prompt_steps(runner, config, tokens)
+                for batch in (8, 64):
+                    got = measure_decode(runner, config, batch, args.prompt_len, args.steps, args.warmup,
+                                         args.prompt_len + 600, None)
+                    entry[f"decode_b{batch}"] = {key: (round(got[key], 3) if isinstance(got[key], float) else got[key])
+                                                 for key in ("ms", "tok_s", "steps_timed", "spread", "launches")}
+                points[f"{name}/{label}"] = entry
+                print(f"[bench] {name}/{label}: {json.dumps(entry)}", file=sys.stderr, flush=True)
+                del runner
+                torch.cuda.empty_cache()
+    main_point = points["1.7b-layers/bemuzen"]["decode_b8"]
+    return {"metric": "decode_tokens_per_s_design", "value": main_point["tok_s"], "unit": "tokens/s", "n_gpus": 1,
+            "steps": main_point["steps_timed"], "warmup": args.warmup, "ms_per_step": main_point["ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (random weights, random token ids)",
+            "config": {"model": f"Bemuzen layers beside Qwen3 layers, {layers} layers each", "global_batch": 8,
+                       "seq_len": args.prompt_len, "parallelism": "single GPU", "vocab": vocab,
+                       "l2": "weights and cache exceed L2 (126 MB) at every size"},
+            "clocks": clocks.summary(), "peaks": {**measured, "kind": peak_kind}, "design": points}
+
+
 def dict_args(args, **changes):
     copy = argparse.Namespace(**vars(args))
     for key, value in changes.items():
@@ -714,6 +811,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in config)")
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--no-points", action="store_true", help="the main point only")
+    parser.add_argument("--design", default=None, choices=("bemuzen",),
+                        help="instead of the default workload: layers of this design beside Qwen3 layers of equal sizes")
     args = parser.parse_args()
 
     if args.gpus != 1:
@@ -729,6 +828,9 @@ def main() -> int:
         print("bench.py needs a CUDA device")
         return 1
     measured, peak_kind = peaks()
+    if args.design:
+        print(json.dumps(run_design(args, measured, peak_kind)))
+        return 0
     record = {"1.7b": run_small, "8b": run_mixed, "32b": run_large}[args.shape](args, measured, peak_kind)
     print(json.dumps(record))
     return 0

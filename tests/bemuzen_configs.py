@@ -48,9 +48,22 @@ BZ_C = {
     ],
 }
 
-CONFIGS = {"A": (BZ_A, 16), "B": (BZ_B, 8), "C": (BZ_C, 32)}
+# Keys and values of one size of 64: in bfloat16 the softmax branch runs on the tensor-core kernels.
+BZ_D = {
+    "architecture": "Bemuzen", "vocab": 157, "width": 128, "logit_scale": 0.3, "norm": {"eps": 1e-5},
+    "embedding": {"bigram": {"buckets": 89, "mul_prev": 2, "mul_cur": 9}},
+    "layers": [
+        _parallel({"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125, "q_temp": {"coef": 0.3, "every": 48}},
+                  {"heads": 2, "dim": 32, "vdim": 64, "decay": [0.98, 0.8]}, 96),
+        _parallel({"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.2, "q_temp": {"coef": 0.5, "every": 100}},
+                  {"heads": 1, "dim": 16, "vdim": 48, "decay": [0.93]}, None),
+    ],
+}
+
+CONFIGS = {"A": (BZ_A, 16), "B": (BZ_B, 8), "C": (BZ_C, 32), "D": (BZ_D, 16)}
 LENGTHS = {
     "A": {"a": 70, "b": 45, "c": 100, "d": 37, "e": 64, "f": 1, "g": 150},
     "B": {"a": 70, "b": 33, "c": 90, "d": 2, "e": 64, "g": 130},
     "C": {"a": 70, "b": 45, "c": 3, "d": 37, "g": 110},
+    "D": {"a": 70, "b": 45, "c": 130, "d": 1, "g": 200},
 }

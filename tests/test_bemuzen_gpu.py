@@ -256,34 +256,45 @@ def paged(tensor_rows, page_size, pages_order, heads, size, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_biased_attention_far_keys_page_borders_and_temperature(dtype):
-    """One request of 333 positions in scattered pages, its last 40 tokens as this step's portion,
-    beside a request that decodes one token and one that starts.  Queries are made to point at chosen
-    keys (a far one at position 3, the keys on both sides of page borders, the newest), so that
-    a kernel that lost one of them would give another row; the temperature steps at multiples of 7."""
+@pytest.mark.parametrize("shape", [(6, 2, 20, 36), (4, 2, 64, 64), (8, 1, 128, 128)])
+def test_biased_attention_far_keys_page_borders_and_temperature(dtype, shape):
+    """Two requests that decode one token (one over 1500 keys, which the tensor-core kernel divides
+    over several blocks) ahead of a request of 333 positions in scattered pages whose last 40 tokens
+    are this step's portion and of one that starts.  Queries are made to point at chosen keys (a far
+    one at position 3, the keys on both sides of page borders, the newest), so that a kernel that
+    lost one of them would give another row; the temperature steps at multiples of 7.  Keys and
+    values of one size of 64 or 128 run on the tensor-core kernels in bfloat16, everything else in
+    the float32-arithmetic kernel."""
     from vllm_from_scratch_b200 import kernels
     g = torch.Generator().manual_seed(5)
-    H, G, d, dv, page, eps, scale = 6, 2, 20, 36, 16, 1e-5, 0.8
+    H, G, d, dv = shape
+    page, eps, scale = 16, 1e-5, 16.0 / d
     coef, every = 0.6, 7
-    lengths, fresh = [333, 50, 3], [40, 1, 3]
+    lengths, fresh = [1500, 50, 333, 3], [1, 1, 40, 3]
     slopes = [plain.bias_slope(h, H) for h in range(H)]
     qw, kw = torch.rand(d, generator=g) + 0.5, torch.rand(d, generator=g) + 0.5
     sequences = []
     for n in lengths:
         q, k, v = torch.randn(n, H, d, generator=g), torch.randn(n, G, d, generator=g), torch.randn(n, G, dv, generator=g)
-        sequences.append((q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double()))
-    q0, k0, _ = sequences[0]
+        sequences.append([q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double()])
+
+    def point(sequence, at, key):             # before the norm: the direction survives it
+        q, k, _ = sequence
+        for head in range(H):
+            q[at, head] = (k[key, head // (H // G)] * kw / qw * 4.0).to(dtype).double()
+
     targets = {300: 3, 301: 15, 302: 16, 303: 17, 304: 255, 305: 256, 306: 304, 332: 0}
-    for at, key in targets.items():            # before the norm: the direction survives it
-        q0[at] = (k0[key, 0] * kw / qw * 4.0).to(dtype).double()
-        q0[at, H // G:] = (k0[key, 1] * kw / qw * 4.0).to(dtype).double()
+    for at, key in targets.items():
+        point(sequences[2], at, key)
+    point(sequences[0], 1499, 3)
     tokens = sum(fresh)
     qkv = torch.zeros(tokens, H * d + G * d + G * dv, dtype=torch.float64)
     want = torch.zeros(tokens, H * dv, dtype=torch.float64)
     positions, slots, tables, starts, row = [], [], [], [0], 0
-    pages_free = list(torch.randperm(64, generator=g).tolist())
-    k_pool = torch.zeros(64, G, page, d, dtype=dtype)
-    v_pool = torch.zeros(64, G, page, dv, dtype=dtype)
+    pool_pages = 160
+    pages_free = list(torch.randperm(pool_pages, generator=g).tolist())
+    k_pool = torch.zeros(pool_pages, G, page, d, dtype=dtype)
+    v_pool = torch.zeros(pool_pages, G, page, dv, dtype=dtype)
     for (q, k, v), n, new in zip(sequences, lengths, fresh):
         table = [pages_free.pop() for _ in range(-(-n // page))]
         tables.append(table)
@@ -302,24 +313,44 @@ def test_biased_attention_far_keys_page_borders_and_temperature(dtype):
             row += 1
         starts.append(row)
     width = max(len(t) for t in tables)
-    table_t = torch.full((3, width), -1, dtype=torch.int32)
+    table_t = torch.full((len(lengths), width), -1, dtype=torch.int32)
     for r, table in enumerate(tables):
         table_t[r, :len(table)] = torch.tensor(table)
     k_d, v_d = dev(k_pool), dev(v_pool)
     q_out = torch.empty(tokens, H * d, dtype=dtype, device="cuda")
     kernels.head_norm_scale_cache(dev(qkv, dtype), i32(positions), i32(slots), dev(qw), dev(kw), eps, (coef, every), q_out,
                                   k_d, v_d, H, G, d, dv, page)
-    out = torch.empty(tokens, H * dv, dtype=dtype, device="cuda")
-    kernels.biased_paged_attention(q_out, k_d, v_d, out, i32(starts), i32(lengths), dev(table_t),
-                                   torch.tensor(slopes, dtype=torch.float32, device="cuda"), H, G, d, dv, page, scale, None)
+    slopes_d = torch.tensor(slopes, dtype=torch.float32, device="cuda")
     tol = 2e-5 if dtype == torch.float32 else 4e-2
-    diff = (out.cpu().double() - want).abs().max(dim=1).values
-    assert float(diff.max()) < tol * float(want.abs().max()), diff
-    # the pointed queries really single their key out in the oracle (the test would notice its loss)
-    _, _, v0 = sequences[0]
-    for at, key in targets.items():          # the last head has the flattest slope: distance costs it least
-        row = at - (lengths[0] - fresh[0])
-        assert float((want[row, (H - 1) * dv:] - v0[key, 1]).abs().max()) < 0.35 * float(v0[key, 1].abs().max()), (at, key)
+
+    def check(out, what):
+        diff = (out.cpu().double() - want).abs().max(dim=1).values
+        assert float(diff.max()) < tol * float(want.abs().max()), (what, diff)
+
+    out = torch.empty(tokens, H * dv, dtype=dtype, device="cuda")
+    kernels.biased_paged_attention(q_out, k_d, v_d, out, i32(starts), i32(lengths), dev(table_t), slopes_d, H, G, d, dv,
+                                   page, scale, None, max(fresh), max(lengths), 2)
+    check(out, "as the engine calls it")
+    out = torch.empty(tokens, H * dv, dtype=dtype, device="cuda")
+    kernels.biased_paged_attention(q_out, k_d, v_d, out, i32(starts), i32(lengths), dev(table_t), slopes_d, H, G, d, dv,
+                                   page, scale, None)
+    check(out, "float32 arithmetic")
+    # the single tokens alone: a decode step
+    out = torch.empty(2, H * dv, dtype=dtype, device="cuda")
+    kernels.biased_paged_attention(q_out[:2], k_d, v_d, out, i32(starts[:3]), i32(lengths[:2]), dev(table_t[:2]), slopes_d,
+                                   H, G, d, dv, page, scale, None, 1, max(lengths), 0)
+    diff = (out.cpu().double() - want[:2]).abs().max()
+    assert float(diff) < tol * float(want.abs().max())
+    # The pointed queries really single their key out in the oracle, so the comparison above would
+    # notice its loss (among hundreds of keys only where the heads are wide enough).  The last head has
+    # the flattest slope: distance costs it least.
+    if d >= 64:
+        v2 = sequences[2][2]
+        for at, key in targets.items():
+            row = 2 + at - (lengths[2] - fresh[2])
+            assert float((want[row, (H - 1) * dv:] - v2[key, G - 1]).abs().max()) < 0.35 * float(v2[key, G - 1].abs().max()), (at, key)
+        far = sequences[0][2][3, G - 1]
+        assert float((want[0, (H - 1) * dv:] - far).abs().max()) < 0.35 * float(far.abs().max())
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -57,6 +57,20 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
 }
+// A pair of float32 weights in [0, 1] as three pairs of bfloat16 whose sum is the pair to the last
+// bit: a product with a bfloat16 matrix, taken once with each piece and summed in float32, is then
+// the product with the float32 weights themselves.
+__device__ __forceinline__ void split_bf16x3(float a, float b, unsigned& hi, unsigned& mid, unsigned& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const float2 hf = __bfloat1622float2(h);
+    const float ra = a - hf.x, rb = b - hf.y;
+    const __nv_bfloat162 m = __floats2bfloat162_rn(ra, rb);
+    const float2 mf = __bfloat1622float2(m);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(ra - mf.x, rb - mf.y);
+    hi = *reinterpret_cast<const unsigned*>(&h);
+    mid = *reinterpret_cast<const unsigned*>(&m);
+    lo = *reinterpret_cast<const unsigned*>(&l);
+}
 __device__ __forceinline__ float quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
     return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -121,12 +135,15 @@ __device__ __forceinline__ void load_q_fragments(unsigned (&qa)[D / 16][4], cons
 // grid (splits, kv heads, requests); every request has exactly one query token,
 // so token index == request index.  Rows of the 16-row fragment are the query
 // heads that share this key/value head (at most 16).
-template <int D>
+// EXACT: the softmax weights stay float32 in the second product (three bfloat16 pieces each, see
+// split_bf16x3), and `slopes` (one per query head, or null) takes slope * (query position - key
+// position) off every score.
+template <int D, bool EXACT = false>
 __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
     const int* __restrict__ seq_lens, const int* __restrict__ block_table, int max_pages, int nq,
-    int nkv, int page_size, float scale_log2, int window, int splits) {
+    int nkv, int page_size, float scale_log2, int window, int splits, const float* __restrict__ slopes) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);
     overlap_trigger();
@@ -155,6 +172,12 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+    // Rows are the group's query heads, each with a slope of its own (in units of log2 e).
+    float slope_a = 0.0f, slope_b = 0.0f;
+    if (EXACT && slopes != nullptr) {
+        if (row_a < group) slope_a = slopes[kv_head * group + row_a] * kLog2e;
+        if (row_b < group) slope_b = slopes[kv_head * group + row_b] * kLog2e;
+    }
 
     auto k_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D; };
     auto v_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D + kKeys * D; };
@@ -195,7 +218,9 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kp = k0 + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const float v = kp < my_end ? s[nt][e] * scale_log2 : -INFINITY;
+                float v = s[nt][e] * scale_log2;
+                if (EXACT) v -= (e < 2 ? slope_a : slope_b) * (float)(seq_len - 1 - kp);
+                if (kp >= my_end) v = -INFINITY;
                 s[nt][e] = v;
                 if (e < 2) max_a = fmaxf(max_a, v); else max_b = fmaxf(max_b, v);
             }
@@ -218,8 +243,16 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
         }
         l_a = l_a * alpha_a + sum_a;
         l_b = l_b * alpha_b + sum_b;
-        unsigned pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
-                          pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+        unsigned pa[4], pm[4], pl[4];
+        if (EXACT) {
+            split_bf16x3(s[0][0], s[0][1], pa[0], pm[0], pl[0]);
+            split_bf16x3(s[0][2], s[0][3], pa[1], pm[1], pl[1]);
+            split_bf16x3(s[1][0], s[1][1], pa[2], pm[2], pl[2]);
+            split_bf16x3(s[1][2], s[1][3], pa[3], pm[3], pl[3]);
+        } else {
+            pa[0] = pack_bf16(s[0][0], s[0][1]); pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[2] = pack_bf16(s[1][0], s[1][1]); pa[3] = pack_bf16(s[1][2], s[1][3]);
+        }
 #pragma unroll
         for (int j = 0; j < D / 16; ++j) {
             o[2 * j][0] *= alpha_a; o[2 * j][1] *= alpha_a; o[2 * j][2] *= alpha_b; o[2 * j][3] *= alpha_b;
@@ -228,6 +261,12 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
             const int chunk_v = j * 2 + (mi >> 1);
             unsigned b[4];
             ldmatrix_x4_trans(b, v_s + key * D + ((chunk_v ^ (key & 7)) << 3));
+            if (EXACT) {        // smallest pieces first
+                mma_bf16(o[2 * j], pl, b[0], b[1]);
+                mma_bf16(o[2 * j + 1], pl, b[2], b[3]);
+                mma_bf16(o[2 * j], pm, b[0], b[1]);
+                mma_bf16(o[2 * j + 1], pm, b[2], b[3]);
+            }
             mma_bf16(o[2 * j], pa, b[0], b[1]);
             mma_bf16(o[2 * j + 1], pa, b[2], b[3]);
         }
@@ -335,12 +374,13 @@ __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const f
 // grid (query tiles, query heads).  A tile is 64 consecutive query tokens of one
 // request, 16 per warp; the request of a tile is found from the tile index as in
 // attention_generic.cu (request r owns tiles [start[r] / 64 + r, start[r+1] / 64 + r + 1)).
-template <int D>
-__global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
+// EXACT and slopes: as in the decode kernel.
+template <int D, bool EXACT = false>
+__global__ void __launch_bounds__(kThreads, EXACT ? 2 : 3) prefill_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, int num_requests, int max_pages, int nq, int nkv,
-    int page_size, float scale_log2, int window, int token_offset) {
+    int page_size, float scale_log2, int window, int token_offset, const float* __restrict__ slopes) {
     // token_offset: row of q and out at which the first of these requests begins (requests ahead of
     // them in the batch are another launch's); query_start holds rows of the whole batch.
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -364,6 +404,7 @@ __global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
     const int past = seq_len - q_len;
     const int head = blockIdx.y;
     const int kv_head = head / (nq / nkv);
+    const float slope = (EXACT && slopes != nullptr) ? slopes[head] * kLog2e : 0.0f;
     const int* table = block_table + (size_t)request * max_pages;
     const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -435,7 +476,8 @@ __global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
                 for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float v = s[nt][e] * scale_log2;
+                        float v = s[nt][e] * scale_log2;
+                        if (EXACT) v -= slope * (float)((e < 2 ? pos_a : pos_b) - (k0 + nt * 8 + (lane & 3) * 2 + (e & 1)));
                         s[nt][e] = v;
                         if (e < 2) max_a = fmaxf(max_a, v); else max_b = fmaxf(max_b, v);
                     }
@@ -448,7 +490,9 @@ __global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
                         const int q_pos = e < 2 ? pos_a : pos_b;
                         bool visible = kp <= q_pos;
                         if (window > 0) visible = visible && (kp > q_pos - window);
-                        const float v = visible ? s[nt][e] * scale_log2 : -INFINITY;
+                        float v = s[nt][e] * scale_log2;
+                        if (EXACT) v -= slope * (float)(q_pos - kp);
+                        if (!visible) v = -INFINITY;
                         s[nt][e] = v;
                         if (e < 2) max_a = fmaxf(max_a, v); else max_b = fmaxf(max_b, v);
                     }
@@ -478,15 +522,28 @@ __global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
             }
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-                const unsigned pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
-                                        pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]),
-                                        pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+                unsigned pa[4], pm[4], pl[4];
+                if (EXACT) {
+                    split_bf16x3(s[2 * kk][0], s[2 * kk][1], pa[0], pm[0], pl[0]);
+                    split_bf16x3(s[2 * kk][2], s[2 * kk][3], pa[1], pm[1], pl[1]);
+                    split_bf16x3(s[2 * kk + 1][0], s[2 * kk + 1][1], pa[2], pm[2], pl[2]);
+                    split_bf16x3(s[2 * kk + 1][2], s[2 * kk + 1][3], pa[3], pm[3], pl[3]);
+                } else {
+                    pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]); pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                    pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]); pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+                }
 #pragma unroll
                 for (int j = 0; j < D / 16; ++j) {
                     const int key = kk * 16 + (mi & 1) * 8 + ri;
                     const int chunk_v = j * 2 + (mi >> 1);
                     unsigned b[4];
                     ldmatrix_x4_trans(b, v_s + key * D + ((chunk_v ^ (key & 7)) << 3));
+                    if (EXACT) {        // smallest pieces first
+                        mma_bf16(o[2 * j], pl, b[0], b[1]);
+                        mma_bf16(o[2 * j + 1], pl, b[2], b[3]);
+                        mma_bf16(o[2 * j], pm, b[0], b[1]);
+                        mma_bf16(o[2 * j + 1], pm, b[2], b[3]);
+                    }
                     mma_bf16(o[2 * j], pa, b[0], b[1]);
                     mma_bf16(o[2 * j + 1], pa, b[2], b[3]);
                 }
@@ -509,19 +566,19 @@ __global__ void __launch_bounds__(kThreads, 3) prefill_attention_kernel(
     }
 }
 
-template <int D>
+template <int D, bool EXACT = false>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o,
                   float* partial_ml, const int* seq_lens, const int* block_table, int num_requests,
                   int max_pages, int nq, int nkv, int page_size, float scale, int window, int splits,
-                  cudaStream_t stream) {
-    auto kernel = decode_attention_kernel<D>;
+                  cudaStream_t stream, const float* slopes = nullptr) {
+    auto kernel = decode_attention_kernel<D, EXACT>;
     const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (status != cudaSuccess) return fail("decode_attention", cudaGetErrorString(status));
     dim3 grid(splits, nkv, num_requests);
     launch_overlapped(kernel, grid, kThreads, smem, stream,
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, partial_o, partial_ml,
-        seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits);
+        seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits, slopes);
     if (int rc = check_launch("decode_attention")) return rc;
     if (splits > 1) {
         launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,
@@ -531,19 +588,19 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     return 0;
 }
 
-template <int D>
+template <int D, bool EXACT = false>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                    const int* query_start, const int* seq_lens, const int* block_table,
                    int num_requests, int num_tokens, int max_pages, int nq, int nkv, int page_size,
-                   float scale, int window, int token_offset, cudaStream_t stream) {
-    auto kernel = prefill_attention_kernel<D>;
+                   float scale, int window, int token_offset, cudaStream_t stream, const float* slopes = nullptr) {
+    auto kernel = prefill_attention_kernel<D, EXACT>;
     const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (status != cudaSuccess) return fail("prefill_attention", cudaGetErrorString(status));
     dim3 grid((num_tokens - token_offset) / 64 + num_requests, nq);
     kernel<<<grid, kThreads, smem, stream>>>(
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, query_start, seq_lens,
-        block_table, num_requests, max_pages, nq, nkv, page_size, scale * kLog2e, window, token_offset);
+        block_table, num_requests, max_pages, nq, nkv, page_size, scale * kLog2e, window, token_offset, slopes);
     return check_launch("prefill_attention");
 }
 

@@ -11,7 +11,11 @@
 // The attention kernel has the launch shape and the masking of the generic kernel in
 // attention_generic.cu: a block is 16 consecutive queries of one request and one query head, found
 // from the block index alone; keys come through the block table in tiles of 32.
-#include "common.cuh"
+//
+// For bfloat16 pages with keys and values of one size of 64, 128 or 256 the two tensor-core kernels of
+// attention_bf16_kernels.cuh serve instead, in their form with float32 weights: the decode kernel
+// (keys split over blocks, merged) for requests that bring one token, the 64-row kernel for portions.
+#include "attention_bf16_kernels.cuh"
 
 namespace b200 {
 
@@ -280,4 +284,55 @@ B200_EXPORT int b200_biased_paged_attention(
                                               num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size, scale,
                                               window, stream);
     return fail("biased_paged_attention", "dtype must be 0 (float32) or 1 (bfloat16)");
+}
+
+// ------------------------------------------------------------- bfloat16 on the tensor cores
+// 1 if the tensor-core kernels with float32 weights take the shape.
+B200_EXPORT int b200_biased_attention_bf16_supports(int nq, int nkv, int d, int dv) {
+    return d == dv && (d == 64 || d == 128 || d == 256) && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16 && nq <= 65535
+               ? 1 : 0;
+}
+
+B200_EXPORT int b200_biased_sm_count() { return b200::sm_count(); }
+
+// One query token per request (row r of q is request r).  With splits > 1, partial_o holds
+// [requests * nq * splits * d] floats and partial_ml [requests * nq * splits * 2] floats of scratch.
+B200_EXPORT int b200_biased_decode_attention_bf16(
+    const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o, float* partial_ml,
+    const int* seq_lens, const int* block_table, const float* slopes, int num_requests, int max_pages, int nq,
+    int nkv, int d, int page_size, float scale, int window, int splits, cudaStream_t stream) {
+    using namespace b200;
+    if (num_requests == 0) return 0;
+    if (!b200_biased_attention_bf16_supports(nq, nkv, d, d)) return fail("biased_decode_attention", "shape not built");
+    if (splits < 1 || nkv > 65535 || num_requests > 65535) return fail("biased_decode_attention", "grid out of range");
+    if (splits > 1 && (partial_o == nullptr || partial_ml == nullptr))
+        return fail("biased_decode_attention", "scratch for the splits is missing");
+#define B200_CASE(D)                                                                                         \
+    if (d == D)                                                                                              \
+        return launch_decode<D, true>(q, k_pages, v_pages, out, partial_o, partial_ml, seq_lens, block_table, \
+                                      num_requests, max_pages, nq, nkv, page_size, scale, window, splits,    \
+                                      stream, slopes);
+    B200_CASE(64) B200_CASE(128) B200_CASE(256)
+#undef B200_CASE
+    return fail("biased_decode_attention", "head_dim not built");
+}
+
+// Portions of prompts: q and out hold num_tokens rows and query_start rows of them; the num_requests
+// requests given here begin at row token_offset.
+B200_EXPORT int b200_biased_prefill_attention_bf16(
+    const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start, const int* seq_lens,
+    const int* block_table, const float* slopes, int num_requests, int num_tokens, int max_pages, int nq, int nkv,
+    int d, int page_size, float scale, int window, int token_offset, cudaStream_t stream) {
+    using namespace b200;
+    if (num_requests == 0 || num_tokens - token_offset <= 0) return 0;
+    if (token_offset < 0) return fail("biased_prefill_attention", "negative token offset");
+    if (!b200_biased_attention_bf16_supports(nq, nkv, d, d)) return fail("biased_prefill_attention", "shape not built");
+#define B200_CASE(D)                                                                                           \
+    if (d == D)                                                                                                \
+        return launch_prefill<D, true>(q, k_pages, v_pages, out, query_start, seq_lens, block_table,           \
+                                       num_requests, num_tokens, max_pages, nq, nkv, page_size, scale, window, \
+                                       token_offset, stream, slopes);
+    B200_CASE(64) B200_CASE(128) B200_CASE(256)
+#undef B200_CASE
+    return fail("biased_prefill_attention", "head_dim not built");
 }

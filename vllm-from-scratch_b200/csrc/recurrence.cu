@@ -7,9 +7,11 @@
 //                              s_t = 1, c = 0, N = key size;
 //   selective scan (SSD)       a_t = exp(-exp(A_log_h) dt_t), dt_t = softplus(dt + bias_h), k_t = B_t,
 //                              q_t = C_t (shared by the heads of a group), v_t = x_t, s_t = dt_t, c = D_h.
-// One thread owns one column of S (its N elements in registers) for the tokens that one request
-// brings in this step; the per-token vectors k and q reach the threads through shared memory in tiles
-// of 16 tokens.  The state is read from the request's slot before the first token and written back
+// A block owns 32 columns of one head's S for the tokens that one request brings in this step: a
+// warp holds an eighth of the rows of those columns in registers (lane = column), the per-token
+// vectors k and q and the block's slice of v reach the warps through shared memory in tiles of 16
+// tokens, every warp leaves its part of y per token in shared memory, and the parts are added in a
+// fixed order.  The state is read from the request's slot before the first token and written back
 // after the last, so a prompt may arrive in any portions; a slot is zeroed by the cache at admission.
 // Everything but the loads of bfloat16 projections is float32.
 #include "common.cuh"
@@ -17,7 +19,8 @@
 namespace b200 {
 
 constexpr int kScanTile = 16;       // tokens staged at a time
-constexpr int kScanColumns = 64;    // columns of S per block
+constexpr int kScanColumns = 32;    // columns of S per block (one per lane)
+constexpr int kScanParts = 8;       // warps per block, each with an eighth of the rows
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
@@ -42,100 +45,139 @@ struct ScanParams {
     const float* skip;          // [H]
 };
 
-template <typename T, int NMAX, bool SSD>
-__global__ void __launch_bounds__(kScanColumns) recurrence_kernel(ScanParams p) {
-    __shared__ __align__(16) float k_s[kScanTile][NMAX];
-    __shared__ __align__(16) float q_s[kScanTile][NMAX];
-    __shared__ float a_s[kScanTile], s_s[kScanTile];
+// NPT: rows of S per thread; the state's rows are padded to 8 * NPT (zeros in k and q there).
+template <typename T, int NPT, bool SSD>
+__global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(ScanParams p) {
+    extern __shared__ __align__(16) float scan_smem[];
+    constexpr int kRows = NPT * kScanParts;
+    float* k_s = scan_smem;                                         // [tile][kRows]
+    float* q_s = k_s + kScanTile * kRows;                           // [tile][kRows]
+    float* v_s = q_s + kScanTile * kRows;                           // [tile][32]
+    float* part_s = v_s + kScanTile * kScanColumns;                 // [tile][parts][32]
+    float* a_s = part_s + kScanTile * kScanParts * kScanColumns;    // [tile]
+    float* s_s = a_s + kScanTile;                                   // [tile]
     const int request = blockIdx.x, head = blockIdx.y;
-    const int column = blockIdx.z * kScanColumns + threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
+    const int column0 = blockIdx.z * kScanColumns, column = column0 + lane;
     const bool live = column < p.dv;
     const int begin = p.query_start[request], end = p.query_start[request + 1];
     if (begin >= end) return;
-    const int n = p.n, n4 = (p.n + 3) & ~3;
+    const int n = p.n;
+    const int row0 = part * NPT;
     float* state = p.state + (((size_t)p.slots[request] * p.heads + head) * n) * p.dv + column;
-    float S[NMAX];
+    float S[NPT];
 #pragma unroll
-    for (int i = 0; i < NMAX; ++i) S[i] = (live && i < n) ? state[(size_t)i * p.dv] : 0.0f;
+    for (int i = 0; i < NPT; ++i) S[i] = (live && row0 + i < n) ? state[(size_t)(row0 + i) * p.dv] : 0.0f;
     const T* proj = (const T*)p.proj;
     const float decay = SSD ? 0.0f : p.decay[head];
     const float skip = SSD ? p.skip[head] : 0.0f;
     const float a_neg = SSD ? -expf(p.a_log[head]) : 0.0f;
     const float dt_bias = SSD ? p.dt_bias[head] : 0.0f;
     const int group = SSD ? head / p.group_heads : 0;
+    const size_t y_stride = (size_t)p.heads * p.dv;
 
     for (int t0 = begin; t0 < end; t0 += kScanTile) {
         const int count = min(kScanTile, end - t0);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < count * n4; idx += blockDim.x) {
-            const int t = idx / n4, i = idx - t * n4;
+        for (int idx = tid; idx < count * kRows; idx += blockDim.x) {
+            const int t = idx / kRows, i = idx - t * kRows;
             const size_t token = (size_t)(t0 + t);
-            if (i >= n) {           // the tail of the last group of four: zeros keep S[i] at zero
-                k_s[t][i] = q_s[t][i] = 0.0f;
-            } else if (SSD) {
-                const float* row = p.xbc + token * p.xbc_width;
-                k_s[t][i] = row[p.off_b + group * n + i];
-                q_s[t][i] = row[p.off_c + group * n + i];
-            } else {
-                const T* row = proj + token * p.stride;
-                k_s[t][i] = silu_f(to_float(row[p.off_k + head * n + i]));
-                q_s[t][i] = silu_f(to_float(row[p.off_q + head * n + i]));
+            float kv = 0.0f, qv = 0.0f;         // rows past n: zeros keep their S at zero
+            if (i < n) {
+                if (SSD) {
+                    const float* row = p.xbc + token * p.xbc_width;
+                    kv = row[p.off_b + group * n + i];
+                    qv = row[p.off_c + group * n + i];
+                } else {
+                    const T* row = proj + token * p.stride;
+                    kv = silu_f(to_float(row[p.off_k + head * n + i]));
+                    qv = silu_f(to_float(row[p.off_q + head * n + i]));
+                }
             }
+            k_s[idx] = kv;
+            q_s[idx] = qv;
         }
-        if (threadIdx.x < count) {
+        for (int idx = tid; idx < count * kScanColumns; idx += blockDim.x) {
+            const int t = idx / kScanColumns, c = idx - t * kScanColumns;
+            const size_t token = (size_t)(t0 + t);
+            float v = 0.0f;
+            if (column0 + c < p.dv) {
+                if (SSD) v = p.xbc[token * p.xbc_width + head * p.dv + column0 + c];
+                else v = silu_f(to_float(proj[token * p.stride + p.off_v + head * p.dv + column0 + c]));
+            }
+            v_s[idx] = v;
+        }
+        if (tid < count) {
             if (SSD) {
-                const float dt = softplus_f(to_float(proj[(size_t)(t0 + threadIdx.x) * p.stride + p.off_dt + head]) + dt_bias);
-                a_s[threadIdx.x] = expf(a_neg * dt);
-                s_s[threadIdx.x] = dt;
+                const float dt = softplus_f(to_float(proj[(size_t)(t0 + tid) * p.stride + p.off_dt + head]) + dt_bias);
+                a_s[tid] = expf(a_neg * dt);
+                s_s[tid] = dt;
             } else {
-                a_s[threadIdx.x] = decay;
-                s_s[threadIdx.x] = 1.0f;
+                a_s[tid] = decay;
+                s_s[tid] = 1.0f;
             }
         }
         __syncthreads();
-        if (!live) continue;
         for (int t = 0; t < count; ++t) {
-            const size_t token = (size_t)(t0 + t);
-            float v;
-            if (SSD) v = p.xbc[token * p.xbc_width + head * p.dv + column];
-            else v = silu_f(to_float(proj[token * p.stride + p.off_v + head * p.dv + column]));
-            const float a = a_s[t], sv = s_s[t] * v;
-            float acc = 0.0f;
+            const float a = a_s[t], sv = s_s[t] * v_s[t * kScanColumns + lane];
+            const float* k_row = k_s + t * kRows + row0;
+            const float* q_row = q_s + t * kRows + row0;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int i = 0; i < NMAX; i += 4) {
-                if (i < n) {        // a group of four that reaches past n meets zeros there
-                    const float4 k4 = *reinterpret_cast<const float4*>(&k_s[t][i]);
-                    const float4 q4 = *reinterpret_cast<const float4*>(&q_s[t][i]);
-                    S[i] = fmaf(a, S[i], k4.x * sv);
-                    S[i + 1] = fmaf(a, S[i + 1], k4.y * sv);
-                    S[i + 2] = fmaf(a, S[i + 2], k4.z * sv);
-                    S[i + 3] = fmaf(a, S[i + 3], k4.w * sv);
-                    acc = fmaf(S[i], q4.x, acc);
-                    acc = fmaf(S[i + 1], q4.y, acc);
-                    acc = fmaf(S[i + 2], q4.z, acc);
-                    acc = fmaf(S[i + 3], q4.w, acc);
-                }
+            for (int i = 0; i < NPT; i += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(k_row + i);
+                const float4 q4 = *reinterpret_cast<const float4*>(q_row + i);
+                S[i] = fmaf(a, S[i], k4.x * sv);
+                S[i + 1] = fmaf(a, S[i + 1], k4.y * sv);
+                S[i + 2] = fmaf(a, S[i + 2], k4.z * sv);
+                S[i + 3] = fmaf(a, S[i + 3], k4.w * sv);
+                acc[0] = fmaf(S[i], q4.x, acc[0]);
+                acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
+                acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
+                acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
             }
-            p.y[token * ((size_t)p.heads * p.dv) + head * p.dv + column] = fmaf(skip, v, acc);
+            part_s[(t * kScanParts + part) * kScanColumns + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        }
+        __syncthreads();
+        for (int idx = tid; idx < count * kScanColumns; idx += blockDim.x) {
+            const int t = idx / kScanColumns, c = idx - t * kScanColumns;
+            if (column0 + c >= p.dv) continue;
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kScanParts; ++w) total += part_s[(t * kScanParts + w) * kScanColumns + c];
+            p.y[(size_t)(t0 + t) * y_stride + head * p.dv + column0 + c] = fmaf(skip, v_s[idx], total);
         }
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < NMAX; ++i)
-            if (i < n) state[(size_t)i * p.dv] = S[i];
+        for (int i = 0; i < NPT; ++i)
+            if (row0 + i < n) state[(size_t)(row0 + i) * p.dv] = S[i];
     }
+}
+
+template <typename T, int NPT, bool SSD>
+int launch_recurrence_rows(const ScanParams& p, int requests, cudaStream_t stream) {
+    auto kernel = recurrence_kernel<T, NPT, SSD>;
+    const size_t smem = sizeof(float) * ((size_t)2 * kScanTile * NPT * kScanParts + kScanTile * kScanColumns +
+                                         (size_t)kScanTile * kScanParts * kScanColumns + 2 * kScanTile);
+    if (smem > 48 * 1024) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("recurrence", cudaGetErrorString(status));
+    }
+    dim3 grid(requests, p.heads, (p.dv + kScanColumns - 1) / kScanColumns);
+    kernel<<<grid, kScanColumns * kScanParts, smem, stream>>>(p);
+    return check_launch("recurrence");
 }
 
 template <typename T, bool SSD>
 int launch_recurrence(const ScanParams& p, int requests, cudaStream_t stream) {
-    dim3 grid(requests, p.heads, (p.dv + kScanColumns - 1) / kScanColumns);
     if (p.heads > 65535) return fail("recurrence", "more than 65535 heads");
-    if (p.n <= 32) recurrence_kernel<T, 32, SSD><<<grid, kScanColumns, 0, stream>>>(p);
-    else if (p.n <= 64) recurrence_kernel<T, 64, SSD><<<grid, kScanColumns, 0, stream>>>(p);
-    else if (p.n <= 128) recurrence_kernel<T, 128, SSD><<<grid, kScanColumns, 0, stream>>>(p);
-    else if (p.n <= 256) recurrence_kernel<T, 256, SSD><<<grid, kScanColumns, 0, stream>>>(p);
-    else return fail("recurrence", "a state of more than 256 rows per head is not built");
-    return check_launch("recurrence");
+    if ((p.dv + kScanColumns - 1) / kScanColumns > 65535) return fail("recurrence", "value heads too wide");
+    if (p.n <= 32) return launch_recurrence_rows<T, 4, SSD>(p, requests, stream);
+    if (p.n <= 64) return launch_recurrence_rows<T, 8, SSD>(p, requests, stream);
+    if (p.n <= 128) return launch_recurrence_rows<T, 16, SSD>(p, requests, stream);
+    if (p.n <= 256) return launch_recurrence_rows<T, 32, SSD>(p, requests, stream);
+    return fail("recurrence", "a state of more than 256 rows per head is not built");
 }
 
 // out[t, c] = silu(bias[c] + sum_i w[c, i] * in[t - (taps - 1 - i), c]) within one request; inputs

@@ -48,7 +48,7 @@ def tensor_map_cache_self_check(count: int = 5000) -> int:
                                                     _I(count)))
 
 
-def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int:
+def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int, sms: int | None = None) -> int:
     """Over how many blocks the keys of one (request, key/value head) are split.
     Three blocks fit on an SM at a time.  Few pairs: the split is chosen so that the blocks fill
     whole rounds of the GPU (a last round with few blocks would leave it idle), with at least 512
@@ -57,7 +57,7 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_seq_len: int) -> int
     to keep the last round from being a few lone blocks, and every split more costs its set-up and
     the merge, which a count of rounds does not see."""
     pairs = max(1, num_requests * num_kv_heads)
-    slots = 3 * sm_count()
+    slots = 3 * (sms if sms is not None else sm_count())
     most = max(1, min(16, max_seq_len // 512))
     if 2 * pairs >= slots:
         # Time in steps of a lone block's tile of 64 keys: a round of blocks that fills the GPU is

@@ -114,24 +114,74 @@ def head_norm_scale_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: tor
          _F(eps), _F(coef), _I(every), _I(_code(dtype)), _stream())
 
 
+# Tests set this to False to drive the float32-arithmetic kernel through the same call.
+USE_TENSOR_CORES = True
+_sms: dict[int, int] = {}
+
+
+def _sm_count() -> int:
+    device = torch.cuda.current_device()
+    if device not in _sms:
+        from ..csrc.build import load_library
+        _sms[device] = int(load_library("attention_bias").b200_biased_sm_count()) or 1
+    return _sms[device]
+
+
 def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                            query_start: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
                            slopes: torch.Tensor | None, num_q_heads: int, num_kv_heads: int, head_dim: int,
-                           value_dim: int, page_size: int, scale: float, window: int | None) -> None:
+                           value_dim: int, page_size: int, scale: float, window: int | None,
+                           max_query_len: int | None = None, max_seq_len: int | None = None,
+                           num_decode: int = 0) -> None:
     """Causal attention of every request's new queries over its pages with the score ``q . k * scale
-    - slopes[h] * (i - j)``; scores, weights and the weighted sum in float32."""
+    - slopes[h] * (i - j)``; scores, weights and the weighted sum in float32.
+
+    bfloat16 with keys and values of one size of 64, 128 or 256 (and ``max_query_len`` and
+    ``max_seq_len`` given): the tensor-core kernels, whose softmax weights enter the second product
+    as three bfloat16 pieces that add up to the float32 weight; requests that bring one token (all
+    of them when ``max_query_len`` is 1, else the first ``num_decode``) go to the kernel that splits
+    the keys over blocks, portions to the 64-row kernel.  Everything else: one kernel in float32
+    arithmetic."""
     tokens = q.shape[0]
     requests = seq_lens.shape[0]
     dtype = q.dtype
+    checked = (
+        _check("queries", q, _RUN, (tokens, num_q_heads * head_dim)),
+        _check("key pages", k_pages, dtype, (None, num_kv_heads, page_size, head_dim)),
+        _check("value pages", v_pages, dtype, (None, num_kv_heads, page_size, value_dim)),
+        _check("attention output", out, dtype, (tokens, num_q_heads * value_dim)),
+        _check("query_start", query_start, torch.int32, (requests + 1,)),
+        _check("seq_lens", seq_lens, torch.int32, (requests,)),
+        _check("block table", block_table, torch.int32, (requests, None)),
+        _check("slopes", slopes, torch.float32, (num_q_heads,), optional=True))
+    if (USE_TENSOR_CORES and dtype == torch.bfloat16 and max_query_len is not None and max_seq_len is not None
+            and head_dim == value_dim and head_dim in (64, 128, 256) and num_q_heads // num_kv_heads <= 16):
+        from .attention_bf16 import decode_splits
+        q_p, k_p, v_p, out_p, start_p, lens_p, table_p, slopes_p = checked
+        single = requests if (max_query_len == 1 and tokens == requests) else num_decode
+        width = block_table.shape[1]
+        if single > 0:
+            splits = decode_splits(single, num_kv_heads, max_seq_len, _sm_count())
+            partial_o = partial_ml = None
+            if splits > 1:
+                partial_o = torch.empty((single * num_q_heads * splits, head_dim), dtype=torch.float32, device=q.device)
+                partial_ml = torch.empty((single * num_q_heads * splits, 2), dtype=torch.float32, device=q.device)
+            _run("attention_bias", "b200_biased_decode_attention_bf16", _P(q_p), _P(k_p), _P(v_p), _P(out_p),
+                 _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
+                 _P(lens_p), _P(table_p), _P(slopes_p), _I(single), _I(width), _I(num_q_heads), _I(num_kv_heads),
+                 _I(head_dim), _I(page_size), _F(scale), _I(window or 0), _I(splits), _stream())
+            if splits > 1:
+                count_launch()
+        if single < requests:
+            # The requests behind the single tokens: their rows of the block table and of the lengths,
+            # the batch's own q, out and query_start (rows of the whole batch).
+            _run("attention_bias", "b200_biased_prefill_attention_bf16", _P(q_p), _P(k_p), _P(v_p), _P(out_p),
+                 _P(start_p + 4 * single), _P(lens_p + 4 * single), _P(table_p + 4 * single * width), _P(slopes_p),
+                 _I(requests - single), _I(tokens), _I(width), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
+                 _I(page_size), _F(scale), _I(window or 0), _I(single), _stream())
+        return
     _run("attention_bias", "b200_biased_paged_attention",
-         _P(_check("queries", q, _RUN, (tokens, num_q_heads * head_dim))),
-         _P(_check("key pages", k_pages, dtype, (None, num_kv_heads, page_size, head_dim))),
-         _P(_check("value pages", v_pages, dtype, (None, num_kv_heads, page_size, value_dim))),
-         _P(_check("attention output", out, dtype, (tokens, num_q_heads * value_dim))),
-         _P(_check("query_start", query_start, torch.int32, (requests + 1,))),
-         _P(_check("seq_lens", seq_lens, torch.int32, (requests,))),
-         _P(_check("block table", block_table, torch.int32, (requests, None))),
-         _P(_check("slopes", slopes, torch.float32, (num_q_heads,), optional=True)),
+         *(_P(address) for address in checked),
          _I(requests), _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
          _I(value_dim), _I(page_size), _F(scale), _I(window or 0), _I(_code(dtype)), _stream())
 

@@ -215,7 +215,8 @@ class BiasedAttention(Mixer):
         attended = torch.empty((tokens, nq * dv), dtype=x.dtype, device=x.device)
         kernels.biased_paged_attention(
             q, cache.keys, cache.values, attended, ctx.query_start, ctx.seq_lens, group.block_table, self.slopes,
-            nq, nkv, d, dv, group.page_size, self.scale, self.window)
+            nq, nkv, d, dv, group.page_size, self.scale, self.window, ctx.max_query_len, ctx.max_seq_len,
+            ctx.num_decode)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
         kernels.gemm(attended, self.out_proj, out)
         return out

@@ -100,11 +100,20 @@ class DecoderModel:
     def num_weight_bytes(self) -> int:
         """Bytes of all distinct weight tensors the parts hold (a tied matrix counts once)."""
         seen, total = set(), 0
-        for part in self._parts():
+        parts = list(self._parts())
+        while parts:
+            part = parts.pop()
             for value in vars(part).values():
                 if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
                     seen.add(value.data_ptr())
                     total += value.numel() * value.element_size()
+                elif isinstance(value, (list, tuple)):
+                    # a part made of parts (mixers side by side) holds them, and maybe tensors, in a list
+                    parts.extend(item for item in value if hasattr(item, "expected_weights"))
+                    for item in value:
+                        if isinstance(item, torch.Tensor) and item.data_ptr() not in seen:
+                            seen.add(item.data_ptr())
+                            total += item.numel() * item.element_size()
         return total
 
     # ------------------------------------------------------------------- cache
