@@ -76,40 +76,60 @@ __global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(S
     const int group = SSD ? head / p.group_heads : 0;
     const size_t y_stride = (size_t)p.heads * p.dv;
 
-    for (int t0 = begin; t0 < end; t0 += kScanTile) {
+    // A tile's inputs are fetched into registers while the tile ahead of it is computed, and reach
+    // shared memory (through silu where the mixer has one) when that tile is done.
+    constexpr int kThreadsHere = kScanColumns * kScanParts;
+    constexpr int kPerKQ = kScanTile * kRows / kThreadsHere;            // elements of k (and of q) per thread
+    constexpr int kPerV = kScanTile * kScanColumns / kThreadsHere;      // elements of v per thread
+    float k_r[kPerKQ], q_r[kPerKQ], v_r[kPerV], a_r = 0.0f, s_r = 0.0f;
+    auto fetch = [&](int t0) {
         const int count = min(kScanTile, end - t0);
-        __syncthreads();
-        for (int idx = tid; idx < count * kRows; idx += blockDim.x) {
+#pragma unroll
+        for (int j = 0; j < kPerKQ; ++j) {
+            const int idx = tid + j * kThreadsHere;
             const int t = idx / kRows, i = idx - t * kRows;
-            const size_t token = (size_t)(t0 + t);
-            float kv = 0.0f, qv = 0.0f;         // rows past n: zeros keep their S at zero
-            if (i < n) {
+            float kv = 0.0f, qv = 0.0f;         // rows past n and tokens past the end: zeros
+            if (t < count && i < n) {
+                const size_t token = (size_t)(t0 + t);
                 if (SSD) {
                     const float* row = p.xbc + token * p.xbc_width;
                     kv = row[p.off_b + group * n + i];
                     qv = row[p.off_c + group * n + i];
                 } else {
                     const T* row = proj + token * p.stride;
-                    kv = silu_f(to_float(row[p.off_k + head * n + i]));
-                    qv = silu_f(to_float(row[p.off_q + head * n + i]));
+                    kv = to_float(row[p.off_k + head * n + i]);
+                    qv = to_float(row[p.off_q + head * n + i]);
                 }
             }
-            k_s[idx] = kv;
-            q_s[idx] = qv;
+            k_r[j] = kv;
+            q_r[j] = qv;
         }
-        for (int idx = tid; idx < count * kScanColumns; idx += blockDim.x) {
+#pragma unroll
+        for (int j = 0; j < kPerV; ++j) {
+            const int idx = tid + j * kThreadsHere;
             const int t = idx / kScanColumns, c = idx - t * kScanColumns;
-            const size_t token = (size_t)(t0 + t);
             float v = 0.0f;
-            if (column0 + c < p.dv) {
+            if (t < count && column0 + c < p.dv) {
+                const size_t token = (size_t)(t0 + t);
                 if (SSD) v = p.xbc[token * p.xbc_width + head * p.dv + column0 + c];
-                else v = silu_f(to_float(proj[token * p.stride + p.off_v + head * p.dv + column0 + c]));
+                else v = to_float(proj[token * p.stride + p.off_v + head * p.dv + column0 + c]);
             }
-            v_s[idx] = v;
+            v_r[j] = v;
         }
-        if (tid < count) {
+        if (SSD && tid < count) a_r = to_float(proj[(size_t)(t0 + tid) * p.stride + p.off_dt + head]);
+    };
+    auto stage = [&]() {
+#pragma unroll
+        for (int j = 0; j < kPerKQ; ++j) {
+            const int idx = tid + j * kThreadsHere;
+            k_s[idx] = SSD ? k_r[j] : silu_f(k_r[j]);
+            q_s[idx] = SSD ? q_r[j] : silu_f(q_r[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < kPerV; ++j) v_s[tid + j * kThreadsHere] = SSD ? v_r[j] : silu_f(v_r[j]);
+        if (tid < kScanTile) {
             if (SSD) {
-                const float dt = softplus_f(to_float(proj[(size_t)(t0 + tid) * p.stride + p.off_dt + head]) + dt_bias);
+                const float dt = softplus_f(a_r + dt_bias);
                 a_s[tid] = expf(a_neg * dt);
                 s_s[tid] = dt;
             } else {
@@ -117,7 +137,16 @@ __global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(S
                 s_s[tid] = 1.0f;
             }
         }
+        (void)s_r;
+    };
+
+    fetch(begin);
+    for (int t0 = begin; t0 < end; t0 += kScanTile) {
+        const int count = min(kScanTile, end - t0);
+        __syncthreads();            // the tile ahead has been added up and stored
+        stage();
         __syncthreads();
+        if (t0 + kScanTile < end) fetch(t0 + kScanTile);
         for (int t = 0; t < count; ++t) {
             const float a = a_s[t], sv = s_s[t] * v_s[t * kScanColumns + lane];
             const float* k_row = k_s + t * kRows + row0;
