@@ -210,3 +210,16 @@ class BemuzenConfig:
     @property
     def num_hidden_layers(self) -> int:
         return len(self.layers)
+
+    def summary(self) -> list[str]:
+        """A few lines that describe the model to a reader of the command line's output."""
+        kinds = [layer.type + ("" if layer.ff is not None else " (no feed-forward)") for layer in self.layers]
+        runs: list[list] = []
+        for kind in kinds:
+            if runs and runs[-1][0] == kind:
+                runs[-1][1] += 1
+            else:
+                runs.append([kind, 1])
+        return [f"{len(self.layers)} layers, width={self.hidden_size}, vocabulary={self.vocab_size}, "
+                f"bigram buckets={self.bigram_buckets}",
+                "order of layers: " + ", ".join(f"{count} x {kind}" for kind, count in runs)]

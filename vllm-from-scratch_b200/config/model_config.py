@@ -192,6 +192,12 @@ class Qwen3Config:
     def kv_width(self) -> int:
         return self.num_key_value_heads * self.head_dim
 
+    def summary(self) -> list[str]:
+        """A few lines that describe the model to a reader of the command line's output."""
+        return [f"{self.num_hidden_layers} layers, hidden={self.hidden_size}, q/kv heads="
+                f"{self.num_attention_heads}/{self.num_key_value_heads}, head_dim={self.head_dim}",
+                f"{self.num_parameters() / 1e9:.3f} G parameters, tied embedding={self.tie_word_embeddings}"]
+
     def num_parameters(self) -> int:
         per_layer = (
             self.hidden_size * (self.q_width + 2 * self.kv_width)

@@ -29,7 +29,7 @@ DEFAULT_PROMPTS = ["1 2 3 4 5 6 7 8", "11 12 13"]
 
 
 def build_parser() -> argparse.ArgumentParser:
-    parser = argparse.ArgumentParser(description="Generate with the B200 Qwen3 engine")
+    parser = argparse.ArgumentParser(description="Generate with the B200 engine (Qwen3 dense, Bemuzen)")
     parser.add_argument("questions", nargs="*", default=None,
                         help="prompts: token ids separated by spaces or commas (text with --text)")
     parser.add_argument("--model-dir", default="models/Qwen3-1.7B",
@@ -113,10 +113,9 @@ def main(argv=None) -> int:
     runner = llm.runner
     config = runner.model_config
     print(f"model: {model_dir} ({config.architecture})")
-    print(f"  {config.num_hidden_layers} layers, hidden={config.hidden_size}, "
-          f"q/kv heads={config.num_attention_heads}/{config.num_key_value_heads}, head_dim={config.head_dim}")
-    print(f"  run dtype {args.dtype}, {config.num_parameters() / 1e9:.3f} G parameters, "
-          f"tied embedding={config.tie_word_embeddings}")
+    for line in config.summary():
+        print(f"  {line}")
+    print(f"  run dtype {args.dtype}, {runner.model.num_weight_bytes() / 1e9:.3f} GB of weights on the device")
     print(f"  cache: {len(runner.storage.groups)} group(s) x {args.num_kv_blocks} pages x {args.block_size} "
           f"positions = {runner.storage.num_bytes() / 1e6:.1f} MB; loaded in {load_seconds:.2f} s")
     print(f"  prefix caching: {'on' if runner.manager.prefix_caching else 'off'}")
