@@ -67,6 +67,155 @@ __global__ void paired_norm_mean_kernel(const T* __restrict__ a, const float* __
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+// Four consecutive elements at a time (16 bytes of float32, 8 of bfloat16); a row of up to 16 elements per
+// thread stays in registers between the passes, so every operand is read once.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned*>(&a);
+    raw.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+__device__ __forceinline__ float dot4(float4 v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+constexpr int kRowSteps = 4;
+
+template <typename T>
+__global__ void add_normed_rmsnorm_vec_kernel(const T* __restrict__ x, const float* __restrict__ x_weight, float x_eps,
+                                              float* __restrict__ residual, const float* __restrict__ weight,
+                                              T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const int out_row = blockIdx.x;
+    const int row = rows ? rows[out_row] : out_row;
+    const size_t base = (size_t)row * hidden;
+    float4 xv[kRowSteps], rv[kRowSteps];
+    float sum_x = 0.0f;
+#pragma unroll
+    for (int step = 0; step < kRowSteps; ++step) {
+        const int i = (step * blockDim.x + threadIdx.x) * 4;
+        if (i < hidden) {
+            xv[step] = load4(x + base + i);
+            rv[step] = load4(residual + base + i);
+            sum_x += dot4(xv[step]);
+        }
+    }
+    const float inv_x = rsqrtf(block_sum(sum_x, scratch) / (float)hidden + x_eps);
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (int step = 0; step < kRowSteps; ++step) {
+        const int i = (step * blockDim.x + threadIdx.x) * 4;
+        if (i < hidden) {
+            const float4 w = load4(x_weight + i);
+            float4 v = rv[step];
+            v.x += xv[step].x * inv_x * w.x; v.y += xv[step].y * inv_x * w.y;
+            v.z += xv[step].z * inv_x * w.z; v.w += xv[step].w * inv_x * w.w;
+            if (rows == nullptr) store4(residual + base + i, v);
+            sum_sq += dot4(v);
+            rv[step] = v;
+        }
+    }
+    if (out == nullptr) return;
+    const float inv = rsqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
+    const size_t out_base = (size_t)out_row * hidden;
+#pragma unroll
+    for (int step = 0; step < kRowSteps; ++step) {
+        const int i = (step * blockDim.x + threadIdx.x) * 4;
+        if (i < hidden) {
+            const float4 w = load4(weight + i), v = rv[step];
+            store4(out + out_base + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+        }
+    }
+}
+
+template <typename T>
+__global__ void paired_norm_mean_vec_kernel(const T* __restrict__ a, const float* __restrict__ wa,
+                                            const T* __restrict__ b, const float* __restrict__ wb,
+                                            T* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float4 av[kRowSteps], bv[kRowSteps];
+    float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+    for (int step = 0; step < kRowSteps; ++step) {
+        const int i = (step * blockDim.x + threadIdx.x) * 4;
+        if (i < hidden) {
+            av[step] = load4(a + base + i);
+            bv[step] = load4(b + base + i);
+            sum_a += dot4(av[step]);
+            sum_b += dot4(bv[step]);
+        }
+    }
+    const float inv_a = rsqrtf(block_sum(sum_a, scratch) / (float)hidden + eps);
+    const float inv_b = rsqrtf(block_sum(sum_b, scratch) / (float)hidden + eps);
+#pragma unroll
+    for (int step = 0; step < kRowSteps; ++step) {
+        const int i = (step * blockDim.x + threadIdx.x) * 4;
+        if (i < hidden) {
+            const float4 u = load4(wa + i), w = load4(wb + i), p = av[step], q = bv[step];
+            store4(out + base + i, make_float4(0.5f * (p.x * inv_a * u.x + q.x * inv_b * w.x),
+                                               0.5f * (p.y * inv_a * u.y + q.y * inv_b * w.y),
+                                               0.5f * (p.z * inv_a * u.z + q.z * inv_b * w.z),
+                                               0.5f * (p.w * inv_a * u.w + q.w * inv_b * w.w)));
+        }
+    }
+}
+
+template <typename T, bool GATE_FIRST>
+__global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
+                                            const float* __restrict__ weight, T* __restrict__ out, int width,
+                                            int group_width, float eps) {
+    __shared__ float scratch[33];
+    const size_t token = blockIdx.x;
+    const int first = blockIdx.y * group_width;
+    const float* y_row = y + token * width + first;
+    const T* g_row = gate + token * gate_stride + first;
+    float4 v[kRowSteps], g[kRowSteps];
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (int step = 0; step < kRowSteps; ++step) {
+        const int i = (step * blockDim.x + threadIdx.x) * 4;
+        if (i < group_width) {
+            v[step] = load4(y_row + i);
+            const float4 z = load4(g_row + i);
+            if (GATE_FIRST) {
+                v[step].x *= z.x * sigmoid_f(z.x); v[step].y *= z.y * sigmoid_f(z.y);
+                v[step].z *= z.z * sigmoid_f(z.z); v[step].w *= z.w * sigmoid_f(z.w);
+            } else {
+                g[step] = make_float4(sigmoid_f(z.x), sigmoid_f(z.y), sigmoid_f(z.z), sigmoid_f(z.w));
+            }
+            sum_sq += dot4(v[step]);
+        }
+    }
+    const float inv = rsqrtf(block_sum(sum_sq, scratch) / (float)group_width + eps);
+    T* o_row = out + token * width + first;
+#pragma unroll
+    for (int step = 0; step < kRowSteps; ++step) {
+        const int i = (step * blockDim.x + threadIdx.x) * 4;
+        if (i < group_width) {
+            const float4 w = load4(weight + first + i), p = v[step];
+            float4 r = make_float4(p.x * inv * w.x, p.y * inv * w.y, p.z * inv * w.z, p.w * inv * w.w);
+            if (!GATE_FIRST) { r.x *= g[step].x; r.y *= g[step].y; r.z *= g[step].z; r.w *= g[step].w; }
+            store4(o_row + i, r);
+        }
+    }
+}
+
+// Threads for a row of `width` elements taken four at a time, at most kRowSteps times a thread; 0 if
+// the row is too long for that.
+inline int vec_threads(int width) {
+    int threads = 32;
+    while (threads < 1024 && threads * 4 * kRowSteps < width) threads *= 2;
+    while (threads < 256 && threads * 4 < width) threads *= 2;        // short rows: one step a thread
+    return threads * 4 * kRowSteps >= width ? threads : 0;
+}
+
 // GATE_FIRST: v = y * silu(z), out = rms_g(v) * w.  Otherwise out = rms_g(y) * w * sigmoid(z).
 template <typename T, bool GATE_FIRST>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
@@ -155,6 +304,17 @@ B200_EXPORT int b200_add_normed_rmsnorm(const void* x, const float* x_weight, fl
     if (num_rows == 0) return 0;
     if (num_rows < 0 || hidden <= 0) return fail("add_normed_rmsnorm", "negative row count or width");
     if ((weight == nullptr) != (out == nullptr)) return fail("add_normed_rmsnorm", "weight and out go together");
+    const uintptr_t addresses = (uintptr_t)x | (uintptr_t)x_weight | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out;
+    if (hidden % 4 == 0 && (addresses & 15) == 0 && vec_threads(hidden) > 0 && (dtype == 0 || dtype == 1)) {
+        const int threads = vec_threads(hidden);
+        if (dtype == 0)
+            add_normed_rmsnorm_vec_kernel<float><<<num_rows, threads, 0, stream>>>(
+                (const float*)x, x_weight, x_eps, residual, weight, (float*)out, rows, hidden, eps);
+        else
+            add_normed_rmsnorm_vec_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+                (const __nv_bfloat16*)x, x_weight, x_eps, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
+        return check_launch("add_normed_rmsnorm");
+    }
     const int threads = row_threads(hidden);
     if (dtype == 0)
         add_normed_rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>(
@@ -172,6 +332,17 @@ B200_EXPORT int b200_paired_norm_mean(const void* a, const float* wa, const void
     using namespace b200;
     if (num_rows == 0) return 0;
     if (num_rows < 0 || hidden <= 0) return fail("paired_norm_mean", "negative row count or width");
+    const uintptr_t addresses = (uintptr_t)a | (uintptr_t)wa | (uintptr_t)b | (uintptr_t)wb | (uintptr_t)out;
+    if (hidden % 4 == 0 && (addresses & 15) == 0 && vec_threads(hidden) > 0 && (dtype == 0 || dtype == 1)) {
+        const int threads = vec_threads(hidden);
+        if (dtype == 0)
+            paired_norm_mean_vec_kernel<float><<<num_rows, threads, 0, stream>>>(
+                (const float*)a, wa, (const float*)b, wb, (float*)out, hidden, eps);
+        else
+            paired_norm_mean_vec_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+                (const __nv_bfloat16*)a, wa, (const __nv_bfloat16*)b, wb, (__nv_bfloat16*)out, hidden, eps);
+        return check_launch("paired_norm_mean");
+    }
     const int threads = row_threads(hidden);
     if (dtype == 0)
         paired_norm_mean_kernel<float><<<num_rows, threads, 0, stream>>>(
@@ -194,8 +365,22 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
     if (tokens < 0 || width <= 0 || groups <= 0 || width % groups) return fail("gated_group_norm", "width must divide into the groups");
     if (groups > 65535) return fail("gated_group_norm", "more than 65535 groups");
     const int group_width = width / groups;
-    const int threads = row_threads(group_width);
     dim3 grid(tokens, groups);
+    const uintptr_t addresses = (uintptr_t)y | (uintptr_t)gate | (uintptr_t)weight | (uintptr_t)out;
+    if (group_width % 4 == 0 && gate_stride % 4 == 0 && (addresses & 15) == 0 && vec_threads(group_width) > 0 &&
+        (dtype == 0 || dtype == 1)) {
+        const int threads = vec_threads(group_width);
+#define B200_VEC(T, FIRST)                                                                                      \
+        gated_group_norm_vec_kernel<T, FIRST><<<grid, threads, 0, stream>>>(y, (const T*)gate, gate_stride, weight, \
+                                                                            (T*)out, width, group_width, eps)
+        if (dtype == 0 && gate_first) B200_VEC(float, true);
+        else if (dtype == 0) B200_VEC(float, false);
+        else if (gate_first) B200_VEC(__nv_bfloat16, true);
+        else B200_VEC(__nv_bfloat16, false);
+#undef B200_VEC
+        return check_launch("gated_group_norm");
+    }
+    const int threads = row_threads(group_width);
 #define B200_CASE(T, FIRST)                                                                             \
     gated_group_norm_kernel<T, FIRST><<<grid, threads, 0, stream>>>(y, (const T*)gate, gate_stride, weight, \
                                                                     (T*)out, width, group_width, eps)
