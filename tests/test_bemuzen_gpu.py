@@ -152,6 +152,27 @@ def test_greedy_generation_through_the_engine(folders, dtype):
     llm.engine.shutdown()
 
 
+def test_preempted_requests_start_again_from_empty_state(folders):
+    """A pool too small for all requests at once: some are preempted, lose their pages and get their
+    slot's states zeroed, and are computed again from their first token; every request still ends
+    with the tokens it gets from a large pool."""
+    import vllm_from_scratch_b200 as engine
+    raw, page_size = CONFIGS["B"]
+    prompts = [helpers.random_tokens(raw["vocab"], n, seed=70 + i) for i, n in enumerate([30, 41, 18, 25])]
+    params = engine.SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
+    results = {}
+    for label, blocks in (("large", 64), ("small", 14)):
+        llm = engine.LLM(str(folders["B"]), dtype="float32", max_model_len=128, block_size=page_size,
+                         num_gpu_blocks=blocks, max_num_seqs=4, max_num_batched_tokens=64)
+        results[label] = llm.generate(prompts, params)
+        if label == "small":
+            assert llm.engine.scheduler.num_preemptions > 0, "the small pool was meant to run out"
+        llm.engine.runner.manager.check_invariants()
+        llm.engine.shutdown()
+    for big, small in zip(results["large"], results["small"]):
+        assert big.token_ids == small.token_ids
+
+
 # ------------------------------------------------------------------- kernels alone
 def dev(tensor, dtype=None):
     return tensor.to("cuda", dtype) if dtype is not None else tensor.to("cuda")
@@ -445,7 +466,7 @@ def test_convolution_and_selective_scan_in_portions(dtype, shape):
             request += [index] * size
         proj = dev(torch.cat(pieces))
         xbc = torch.empty(starts[-1], channels, device="cuda")
-        kernels.causal_conv_silu(proj, inner, dev(conv_w), dev(conv_b), conv_state, i32(request), i32(starts), i32(order), xbc)
+        kernels.causal_conv_silu(proj, inner, dev(conv_w.t().contiguous()), dev(conv_b), conv_state, i32(request), i32(starts), i32(order), xbc)
         y = torch.empty(starts[-1], inner, device="cuda")
         kernels.selective_scan(xbc, proj, inner + channels, dev(dt_bias), dev(a_log), dev(skip), i32(starts), i32(order),
                                state, y, H, G, N, dv)

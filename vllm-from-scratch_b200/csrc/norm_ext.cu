@@ -134,11 +134,29 @@ __global__ void add_normed_rmsnorm_vec_kernel(const T* __restrict__ x, const flo
     }
 }
 
+// Two sums over the block at once; every thread gets both.  `scratch` holds 66 floats.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) { scratch[warp] = a; scratch[33 + warp] = b; }
+    __syncthreads();
+    if (warp == 0) {
+        float ta = lane < warps ? scratch[lane] : 0.0f, tb = lane < warps ? scratch[33 + lane] : 0.0f;
+        ta = warp_sum(ta);
+        tb = warp_sum(tb);
+        if (lane == 0) { scratch[32] = ta; scratch[65] = tb; }
+    }
+    __syncthreads();
+    return make_float2(scratch[32], scratch[65]);
+}
+
 template <typename T>
 __global__ void paired_norm_mean_vec_kernel(const T* __restrict__ a, const float* __restrict__ wa,
                                             const T* __restrict__ b, const float* __restrict__ wb,
                                             T* __restrict__ out, int hidden, float eps) {
-    __shared__ float scratch[33];
+    __shared__ float scratch[66];
     const size_t base = (size_t)blockIdx.x * hidden;
     float4 av[kRowSteps], bv[kRowSteps];
     float sum_a = 0.0f, sum_b = 0.0f;
@@ -152,8 +170,9 @@ __global__ void paired_norm_mean_vec_kernel(const T* __restrict__ a, const float
             sum_b += dot4(bv[step]);
         }
     }
-    const float inv_a = rsqrtf(block_sum(sum_a, scratch) / (float)hidden + eps);
-    const float inv_b = rsqrtf(block_sum(sum_b, scratch) / (float)hidden + eps);
+    const float2 sums = block_sum2(sum_a, sum_b, scratch);
+    const float inv_a = rsqrtf(sums.x / (float)hidden + eps);
+    const float inv_b = rsqrtf(sums.y / (float)hidden + eps);
 #pragma unroll
     for (int step = 0; step < kRowSteps; ++step) {
         const int i = (step * blockDim.x + threadIdx.x) * 4;

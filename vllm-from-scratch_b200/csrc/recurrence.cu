@@ -7,8 +7,9 @@
 //                              s_t = 1, c = 0, N = key size;
 //   selective scan (SSD)       a_t = exp(-exp(A_log_h) dt_t), dt_t = softplus(dt + bias_h), k_t = B_t,
 //                              q_t = C_t (shared by the heads of a group), v_t = x_t, s_t = dt_t, c = D_h.
-// A block owns 32 columns of one head's S for the tokens that one request brings in this step: a
-// warp holds an eighth of the rows of those columns in registers (lane = column), the per-token
+// A block owns 32, 16 or 8 columns of one head's S for the tokens that one request brings in this
+// step (fewer columns, and so more blocks, where a launch would otherwise leave SMs idle): its 256
+// threads hold the rows of those columns in registers, 8, 16 or 32 parts of the rows, the per-token
 // vectors k and q and the block's slice of v reach the warps through shared memory in tiles of 16
 // tokens, every warp leaves its part of y per token in shared memory, and the parts are added in a
 // fixed order.  The state is read from the request's slot before the first token and written back
@@ -19,10 +20,14 @@
 namespace b200 {
 
 constexpr int kScanTile = 16;       // tokens staged at a time
-constexpr int kScanColumns = 32;    // columns of S per block (one per lane)
-constexpr int kScanParts = 8;       // warps per block, each with an eighth of the rows
+constexpr int kScanThreads = 256;   // eight warps; a warp is COLS columns times 32 / COLS parts of the rows
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+// The activation of a projection or of the convolution in the mode whose projections are bfloat16:
+// the hardware's exponential and division (a few units in the last place of float32, far inside what
+// the rounding of the operand to bfloat16 leaves); the 32-bit mode takes the precise forms.
+template <typename T> __device__ __forceinline__ float silu_of(float z) { return silu_f(z); }
+template <> __device__ __forceinline__ float silu_of<__nv_bfloat16>(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
 struct ScanParams {
@@ -45,10 +50,12 @@ struct ScanParams {
     const float* skip;          // [H]
 };
 
-// NPT: rows of S per thread; the state's rows are padded to 8 * NPT (zeros in k and q there).
-template <typename T, int NPT, bool SSD>
-__global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(ScanParams p) {
+// NPT: rows of S per thread; COLS: columns per block.  The state's rows are padded to NPT * 256 / COLS
+// (zeros in k and q there).
+template <typename T, int NPT, int COLS, bool SSD>
+__global__ void __launch_bounds__(kScanThreads) recurrence_kernel(ScanParams p) {
     extern __shared__ __align__(16) float scan_smem[];
+    constexpr int kScanColumns = COLS, kScanParts = kScanThreads / COLS;
     constexpr int kRows = NPT * kScanParts;
     float* k_s = scan_smem;                                         // [tile][kRows]
     float* q_s = k_s + kScanTile * kRows;                           // [tile][kRows]
@@ -57,7 +64,7 @@ __global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(S
     float* a_s = part_s + kScanTile * kScanParts * kScanColumns;    // [tile]
     float* s_s = a_s + kScanTile;                                   // [tile]
     const int request = blockIdx.x, head = blockIdx.y;
-    const int tid = threadIdx.x, lane = tid & 31, part = tid >> 5;
+    const int tid = threadIdx.x, lane = tid % COLS, part = tid / COLS;      // lane: the thread's column
     const int column0 = blockIdx.z * kScanColumns, column = column0 + lane;
     const bool live = column < p.dv;
     const int begin = p.query_start[request], end = p.query_start[request + 1];
@@ -78,9 +85,9 @@ __global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(S
 
     // A tile's inputs are fetched into registers while the tile ahead of it is computed, and reach
     // shared memory (through silu where the mixer has one) when that tile is done.
-    constexpr int kThreadsHere = kScanColumns * kScanParts;
+    constexpr int kThreadsHere = kScanThreads;
     constexpr int kPerKQ = kScanTile * kRows / kThreadsHere;            // elements of k (and of q) per thread
-    constexpr int kPerV = kScanTile * kScanColumns / kThreadsHere;      // elements of v per thread
+    constexpr int kPerV = (kScanTile * kScanColumns + kThreadsHere - 1) / kThreadsHere;   // of v (not every thread has one)
     float k_r[kPerKQ], q_r[kPerKQ], v_r[kPerV], a_r = 0.0f, s_r = 0.0f;
     auto fetch = [&](int t0) {
         const int count = min(kScanTile, end - t0);
@@ -109,7 +116,7 @@ __global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(S
             const int idx = tid + j * kThreadsHere;
             const int t = idx / kScanColumns, c = idx - t * kScanColumns;
             float v = 0.0f;
-            if (t < count && column0 + c < p.dv) {
+            if (t < count && column0 + c < p.dv) {      // t >= kScanTile for threads without an element
                 const size_t token = (size_t)(t0 + t);
                 if (SSD) v = p.xbc[token * p.xbc_width + head * p.dv + column0 + c];
                 else v = to_float(proj[token * p.stride + p.off_v + head * p.dv + column0 + c]);
@@ -122,11 +129,12 @@ __global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(S
 #pragma unroll
         for (int j = 0; j < kPerKQ; ++j) {
             const int idx = tid + j * kThreadsHere;
-            k_s[idx] = SSD ? k_r[j] : silu_f(k_r[j]);
-            q_s[idx] = SSD ? q_r[j] : silu_f(q_r[j]);
+            k_s[idx] = SSD ? k_r[j] : silu_of<T>(k_r[j]);
+            q_s[idx] = SSD ? q_r[j] : silu_of<T>(q_r[j]);
         }
 #pragma unroll
-        for (int j = 0; j < kPerV; ++j) v_s[tid + j * kThreadsHere] = SSD ? v_r[j] : silu_f(v_r[j]);
+        for (int j = 0; j < kPerV; ++j)
+            if (tid + j * kThreadsHere < kScanTile * kScanColumns) v_s[tid + j * kThreadsHere] = SSD ? v_r[j] : silu_of<T>(v_r[j]);
         if (tid < kScanTile) {
             if (SSD) {
                 const float dt = softplus_f(a_r + dt_bias);
@@ -184,32 +192,50 @@ __global__ void __launch_bounds__(kScanColumns * kScanParts) recurrence_kernel(S
     }
 }
 
-template <typename T, int NPT, bool SSD>
+template <typename T, int NPT, int COLS, bool SSD>
 int launch_recurrence_rows(const ScanParams& p, int requests, cudaStream_t stream) {
-    auto kernel = recurrence_kernel<T, NPT, SSD>;
-    const size_t smem = sizeof(float) * ((size_t)2 * kScanTile * NPT * kScanParts + kScanTile * kScanColumns +
-                                         (size_t)kScanTile * kScanParts * kScanColumns + 2 * kScanTile);
+    auto kernel = recurrence_kernel<T, NPT, COLS, SSD>;
+    constexpr int kRows = NPT * kScanThreads / COLS;
+    const size_t smem = sizeof(float) * ((size_t)2 * kScanTile * kRows + kScanTile * COLS +
+                                         (size_t)kScanTile * kScanThreads + 2 * kScanTile);
     if (smem > 48 * 1024) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("recurrence", cudaGetErrorString(status));
     }
-    dim3 grid(requests, p.heads, (p.dv + kScanColumns - 1) / kScanColumns);
-    kernel<<<grid, kScanColumns * kScanParts, smem, stream>>>(p);
+    dim3 grid(requests, p.heads, (p.dv + COLS - 1) / COLS);
+    kernel<<<grid, kScanThreads, smem, stream>>>(p);
     return check_launch("recurrence");
 }
 
 template <typename T, bool SSD>
 int launch_recurrence(const ScanParams& p, int requests, cudaStream_t stream) {
     if (p.heads > 65535) return fail("recurrence", "more than 65535 heads");
-    if ((p.dv + kScanColumns - 1) / kScanColumns > 65535) return fail("recurrence", "value heads too wide");
-    if (p.n <= 32) return launch_recurrence_rows<T, 4, SSD>(p, requests, stream);
-    if (p.n <= 64) return launch_recurrence_rows<T, 8, SSD>(p, requests, stream);
-    if (p.n <= 128) return launch_recurrence_rows<T, 16, SSD>(p, requests, stream);
-    if (p.n <= 256) return launch_recurrence_rows<T, 32, SSD>(p, requests, stream);
-    return fail("recurrence", "a state of more than 256 rows per head is not built");
+    if ((p.dv + 7) / 8 > 65535) return fail("recurrence", "value heads too wide");
+    if (p.n > 256) return fail("recurrence", "a state of more than 256 rows per head is not built");
+    // Fewer columns a block while the launch would leave SMs without a block, as long as a thread
+    // keeps four rows at least (64 rows of state for 16 columns, 128 for 8).
+    const long long sms = sm_count() > 0 ? sm_count() : 1;
+    int cols = 32;
+    while (cols > 8 && (long long)requests * p.heads * ((p.dv + cols - 1) / cols) < sms && p.n > 32 * (32 / cols)) cols /= 2;
+#define B200_ROWS(NPT, COLS) return launch_recurrence_rows<T, NPT, COLS, SSD>(p, requests, stream)
+    if (cols == 32) {
+        if (p.n <= 32) B200_ROWS(4, 32);
+        if (p.n <= 64) B200_ROWS(8, 32);
+        if (p.n <= 128) B200_ROWS(16, 32);
+        B200_ROWS(32, 32);
+    }
+    if (cols == 16) {
+        if (p.n <= 64) B200_ROWS(4, 16);
+        if (p.n <= 128) B200_ROWS(8, 16);
+        B200_ROWS(16, 16);
+    }
+    if (p.n <= 128) B200_ROWS(4, 8);
+    B200_ROWS(8, 8);
+#undef B200_ROWS
 }
 
-// out[t, c] = silu(bias[c] + sum_i w[c, i] * in[t - (taps - 1 - i), c]) within one request; inputs
+// out[t, c] = silu(bias[c] + sum_i w[i, c] * in[t - (taps - 1 - i), c]) within one request (the taps'
+// weights are handed over tap by tap, [taps, channels], so that a warp reads them side by side); inputs
 // before the step's portion come from the request's state (its last taps - 1 inputs, oldest first,
 // zeros before the sequence's start).
 template <typename T>
@@ -228,9 +254,48 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int stride, in
             float v;
             if (place - back >= 0) v = to_float(in[(size_t)(token - back) * stride + offset + c]);
             else v = kept[(size_t)(taps - 1 + place - back) * channels + c];
-            acc = fmaf(w[(size_t)c * taps + i], v, acc);
+            acc = fmaf(w[(size_t)i * channels + c], v, acc);
         }
-        out[(size_t)token * channels + c] = silu_f(acc);
+        out[(size_t)token * channels + c] = silu_of<T>(acc);
+    }
+}
+
+// The same for four consecutive channels a thread (8- or 16-byte loads, one 16-byte store).
+template <typename T>
+__global__ void causal_conv_silu_vec_kernel(const T* __restrict__ in, int stride, int offset, const float* __restrict__ w,
+                                            const float* __restrict__ bias, const float* __restrict__ state,
+                                            const int* __restrict__ token_request, const int* __restrict__ query_start,
+                                            const int* __restrict__ slots, float* __restrict__ out, int channels, int taps) {
+    const int token = blockIdx.x;
+    const int request = token_request[token];
+    const int place = token - query_start[request];
+    const float* kept = state + (size_t)slots[request] * (taps - 1) * channels;
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < channels; c += gridDim.y * blockDim.x * 4) {
+        float4 acc = *reinterpret_cast<const float4*>(bias + c);
+        for (int i = 0; i < taps; ++i) {
+            const int back = taps - 1 - i;
+            float4 v;
+            if (place - back >= 0) {
+                const T* src = in + (size_t)(token - back) * stride + offset + c;
+                if (sizeof(T) == 4) {
+                    v = *reinterpret_cast<const float4*>(src);
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                    v = make_float4(lo.x, lo.y, hi.x, hi.y);
+                }
+            } else {
+                v = *reinterpret_cast<const float4*>(kept + (size_t)(taps - 1 + place - back) * channels + c);
+            }
+            const float4 w4 = *reinterpret_cast<const float4*>(w + (size_t)i * channels + c);
+            acc.x = fmaf(w4.x, v.x, acc.x);
+            acc.y = fmaf(w4.y, v.y, acc.y);
+            acc.z = fmaf(w4.z, v.z, acc.z);
+            acc.w = fmaf(w4.w, v.w, acc.w);
+        }
+        *reinterpret_cast<float4*>(out + (size_t)token * channels + c) =
+            make_float4(silu_of<T>(acc.x), silu_of<T>(acc.y), silu_of<T>(acc.z), silu_of<T>(acc.w));
     }
 }
 
@@ -305,7 +370,7 @@ B200_EXPORT int b200_selective_scan(const float* xbc, int xbc_width, const void*
 }
 
 // The convolution reads the state, the second kernel replaces it: call them in this order.
-// in: [T, stride] with the channels at column `offset`; w float32 [channels, taps] (last column: the
+// in: [T, stride] with the channels at column `offset`; w float32 [taps, channels] (last row: the
 // current token); state float32 [slots + 1, taps - 1, channels]; out float32 [T, channels].
 B200_EXPORT int b200_causal_conv_silu(const void* in, int stride, int offset, const float* w, const float* bias,
                                       float* state, const int* token_request, const int* query_start,
@@ -317,7 +382,20 @@ B200_EXPORT int b200_causal_conv_silu(const void* in, int stride, int offset, co
     if (dtype != 0 && dtype != 1) return fail("causal_conv_silu", "dtype must be 0 (float32) or 1 (bfloat16)");
     const int threads = 128;
     const int tiles = min((channels + threads - 1) / threads, 65535);
-    if (dtype == 0)
+    const uintptr_t addresses = (uintptr_t)in | (uintptr_t)w | (uintptr_t)bias | (uintptr_t)state | (uintptr_t)out;
+    if (channels % 4 == 0 && stride % 4 == 0 && offset % 4 == 0 && (addresses & 15) == 0) {
+        // A block first finds its token's request, slot and place (three loads in a row): few blocks a
+        // token, each with many channels, so that this is paid once for much work.
+        const int most = (channels / 4 + 2 * threads - 1) / (2 * threads);
+        const int sms = sm_count() > 0 ? sm_count() : 1;
+        const int wide = max(1, min(most, (2 * sms + tokens - 1) / tokens));
+        if (dtype == 0)
+            causal_conv_silu_vec_kernel<float><<<dim3(tokens, wide), 2 * threads, 0, stream>>>(
+                (const float*)in, stride, offset, w, bias, state, token_request, query_start, slots, out, channels, taps);
+        else
+            causal_conv_silu_vec_kernel<__nv_bfloat16><<<dim3(tokens, wide), 2 * threads, 0, stream>>>(
+                (const __nv_bfloat16*)in, stride, offset, w, bias, state, token_request, query_start, slots, out, channels, taps);
+    } else if (dtype == 0)
         causal_conv_silu_kernel<float><<<dim3(tokens, tiles), threads, 0, stream>>>(
             (const float*)in, stride, offset, w, bias, state, token_request, query_start, slots, out, channels, taps);
     else

@@ -232,12 +232,13 @@ def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bia
 def causal_conv_silu(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor,
                      state: torch.Tensor, token_request: torch.Tensor, query_start: torch.Tensor,
                      slots: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[t, c] = silu(bias[c] + sum_i weight[c, i] * in[t - (taps - 1 - i), c])`` over the columns
-    ``offset .. offset + channels`` of ``proj``, within each request; what lies before a step's
+    """``out[t, c] = silu(bias[c] + sum_i weight[i, c] * in[t - (taps - 1 - i), c])`` over the columns
+    ``offset .. offset + channels`` of ``proj``, within each request (``weight`` is ``[taps, channels]``:
+    a checkpoint's ``[channels, taps]`` transposed, the last row for the current token); what lies before a step's
     portion comes from ``state`` (float32 ``[slots + 1, taps - 1, channels]``: the request's last
     inputs, oldest first), which then receives the last inputs of this step."""
     tokens = proj.shape[0]
-    channels, taps = weight.shape
+    taps, channels = weight.shape
     requests = slots.shape[0]
     _run("recurrence", "b200_causal_conv_silu",
          _P(_check("projection", proj, _RUN, (tokens, None))), _I(proj.shape[1]), _I(offset),

@@ -131,7 +131,8 @@ class SelectiveScan(Mixer):
     def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
         w_in, conv, conv_b, dt_bias, a_log, skip, norm, out = self.names
         self.in_proj = tensors[w_in].contiguous()
-        self.conv, self.conv_bias = tensors[conv].contiguous(), tensors[conv_b]
+        # tap by tap, [taps, channels]: the kernel's warps read a tap's weights side by side
+        self.conv, self.conv_bias = tensors[conv].t().contiguous(), tensors[conv_b]
         self.dt_bias, self.a_log, self.skip = tensors[dt_bias], tensors[a_log], tensors[skip]
         self.norm = tensors[norm]
         self.out_proj = tensors[out].contiguous()
