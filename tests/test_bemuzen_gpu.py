@@ -113,6 +113,24 @@ def test_mixed_batches_with_few_pages_and_slots(folders, references, name, seed,
     assert runner.manager.stats()["requests"] == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_long_portions_run_in_segments(folders, references, name, dtype, monkeypatch):
+    """Portions of 32 tokens and more are cut into segments of about 16 that run side by side, each from
+    an empty state, and are then corrected by the state they should have started from: the same rows,
+    for whole prompts, for portions that start in the middle of a sequence, and beside single tokens."""
+    from vllm_from_scratch_b200.kernels import mixing
+    monkeypatch.setattr(mixing, "SCAN_SEGMENT", 16)
+    raw, page_size = CONFIGS[name]
+    sequences, expected = references[name]
+    for label, steps in (("whole", helpers.cut_whole(LENGTHS[name])),
+                         ("mixed", helpers.cut_mixed(LENGTHS[name], seed=5, live=3, sizes=(2, 33, 40, 64, 100)))):
+        pages = sum(sorted((-(-n // page_size) for n in LENGTHS[name].values()), reverse=True)[:3])
+        runner = make_runner(folders[name], dtype, page_size, pages, max_requests=3)
+        results = helpers.run_schedule(runner, sequences, steps)
+        compare(results, expected, dtype, f"{name}/segments/{label}/{dtype}")
+
+
 def test_long_decoding_keeps_the_state(folders, references):
     """A short prompt and 140 tokens decoded one by one through recurrences and the convolution."""
     raw, page_size = CONFIGS["A"]

@@ -15,6 +15,14 @@
 // fixed order.  The state is read from the request's slot before the first token and written back
 // after the last, so a prompt may arrive in any portions; a slot is zeroed by the cache at admission.
 // Everything but the loads of bfloat16 projections is float32.
+//
+// A long portion would be one long chain of dependent steps in few blocks.  It is therefore cut into
+// segments of seg_len tokens that run side by side (mode 1): a request's first segment starts from its
+// state, the others from zero, and each leaves the state it ends with and the product of its decays.
+// One small kernel then walks over a request's segments, turns what each left into the state it
+// should have started from (C_s = D_{s-1} C_{s-1} + S_{s-1}) and stores the last one in the slot; and
+// the segments run once more (mode 2) to add what that state contributes, y_t += (a_first .. a_t) C^T q_t,
+// in which nothing depends on the token ahead.
 #include "common.cuh"
 
 namespace b200 {
@@ -48,6 +56,11 @@ struct ScanParams {
     const float* dt_bias;       // [H]
     const float* a_log;         // [H]
     const float* skip;          // [H]
+    // A long portion in segments (mode 1 and 2, see below): tokens per segment, segments a request at
+    // most, the segments' states [R * segs, H, N, dv] and decays [R * segs, H].
+    int mode, seg_len, segs;
+    float* seg_state;
+    float* seg_decay;
 };
 
 // NPT: rows of S per thread; COLS: columns per block.  The state's rows are padded to NPT * 256 / COLS
@@ -63,18 +76,31 @@ __global__ void __launch_bounds__(kScanThreads) recurrence_kernel(ScanParams p) 
     float* part_s = v_s + kScanTile * kScanColumns;                 // [tile][parts][32]
     float* a_s = part_s + kScanTile * kScanParts * kScanColumns;    // [tile]
     float* s_s = a_s + kScanTile;                                   // [tile]
-    const int request = blockIdx.x, head = blockIdx.y;
+    const int segs = p.mode == 0 ? 1 : p.segs;
+    const int request = blockIdx.x / segs, segment = blockIdx.x - request * segs, head = blockIdx.y;
+    const bool correct = p.mode == 2;
     const int tid = threadIdx.x, lane = tid % COLS, part = tid / COLS;      // lane: the thread's column
     const int column0 = blockIdx.z * kScanColumns, column = column0 + lane;
     const bool live = column < p.dv;
-    const int begin = p.query_start[request], end = p.query_start[request + 1];
+    int begin = p.query_start[request], end = p.query_start[request + 1];
+    if (p.mode != 0) {
+        begin += segment * p.seg_len;
+        end = min(end, begin + p.seg_len);
+        if (correct && segment == 0) return;        // the first segment started from the true state
+    }
     if (begin >= end) return;
     const int n = p.n;
     const int row0 = part * NPT;
     float* state = p.state + (((size_t)p.slots[request] * p.heads + head) * n) * p.dv + column;
+    float* left = p.mode == 0 ? state      // where the state goes at the end (mode 2: where it comes from)
+                              : p.seg_state + (((size_t)blockIdx.x * p.heads + head) * n) * p.dv + column;
+    const float* from = correct ? left : state;
+    const bool starts_empty = p.mode == 1 && segment > 0;
     float S[NPT];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) S[i] = (live && row0 + i < n) ? state[(size_t)(row0 + i) * p.dv] : 0.0f;
+    for (int i = 0; i < NPT; ++i)
+        S[i] = (live && row0 + i < n && !starts_empty) ? from[(size_t)(row0 + i) * p.dv] : 0.0f;
+    float decays = 1.0f;            // product of the decays of the tokens so far
     const T* proj = (const T*)p.proj;
     const float decay = SSD ? 0.0f : p.decay[head];
     const float skip = SSD ? p.skip[head] : 0.0f;
@@ -98,13 +124,13 @@ __global__ void __launch_bounds__(kScanThreads) recurrence_kernel(ScanParams p) 
             float kv = 0.0f, qv = 0.0f;         // rows past n and tokens past the end: zeros
             if (t < count && i < n) {
                 const size_t token = (size_t)(t0 + t);
-                if (SSD) {
+                if (SSD) {          // the second pass of a portion in segments needs q alone
                     const float* row = p.xbc + token * p.xbc_width;
-                    kv = row[p.off_b + group * n + i];
+                    if (!correct) kv = row[p.off_b + group * n + i];
                     qv = row[p.off_c + group * n + i];
                 } else {
                     const T* row = proj + token * p.stride;
-                    kv = to_float(row[p.off_k + head * n + i]);
+                    if (!correct) kv = to_float(row[p.off_k + head * n + i]);
                     qv = to_float(row[p.off_q + head * n + i]);
                 }
             }
@@ -116,7 +142,7 @@ __global__ void __launch_bounds__(kScanThreads) recurrence_kernel(ScanParams p) 
             const int idx = tid + j * kThreadsHere;
             const int t = idx / kScanColumns, c = idx - t * kScanColumns;
             float v = 0.0f;
-            if (t < count && column0 + c < p.dv) {      // t >= kScanTile for threads without an element
+            if (t < count && column0 + c < p.dv && !correct) {      // t >= kScanTile for threads without an element
                 const size_t token = (size_t)(t0 + t);
                 if (SSD) v = p.xbc[token * p.xbc_width + head * p.dv + column0 + c];
                 else v = to_float(proj[token * p.stride + p.off_v + head * p.dv + column0 + c]);
@@ -160,6 +186,19 @@ __global__ void __launch_bounds__(kScanThreads) recurrence_kernel(ScanParams p) 
             const float* k_row = k_s + t * kRows + row0;
             const float* q_row = q_s + t * kRows + row0;
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            decays *= a;
+            if (correct) {
+#pragma unroll
+                for (int i = 0; i < NPT; i += 4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(q_row + i);
+                    acc[0] = fmaf(S[i], q4.x, acc[0]);
+                    acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
+                    acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
+                    acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
+                }
+                part_s[(t * kScanParts + part) * kScanColumns + lane] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * decays;
+                continue;
+            }
 #pragma unroll
             for (int i = 0; i < NPT; i += 4) {
                 const float4 k4 = *reinterpret_cast<const float4*>(k_row + i);
@@ -182,13 +221,45 @@ __global__ void __launch_bounds__(kScanThreads) recurrence_kernel(ScanParams p) 
             float total = 0.0f;
 #pragma unroll
             for (int w = 0; w < kScanParts; ++w) total += part_s[(t * kScanParts + w) * kScanColumns + c];
-            p.y[(size_t)(t0 + t) * y_stride + head * p.dv + column0 + c] = fmaf(skip, v_s[idx], total);
+            float* y = p.y + (size_t)(t0 + t) * y_stride + head * p.dv + column0 + c;
+            if (correct) *y += total;
+            else *y = fmaf(skip, v_s[idx], total);
         }
     }
+    if (correct) return;
     if (live) {
 #pragma unroll
         for (int i = 0; i < NPT; ++i)
-            if (row0 + i < n) state[(size_t)(row0 + i) * p.dv] = S[i];
+            if (row0 + i < n) left[(size_t)(row0 + i) * p.dv] = S[i];
+    }
+    if (p.mode == 1 && tid == 0 && blockIdx.z == 0) p.seg_decay[(size_t)blockIdx.x * p.heads + head] = decays;
+}
+
+// After the segments have run side by side: per request, segment after segment, what a segment left
+// (the state it ends with when started from zero; the first one's from the true state) becomes the
+// state it should have started from, and the last state goes to the request's slot.  One thread an
+// element of a head's state.
+__global__ void carry_states_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_decay,
+                                    float* __restrict__ state, const int* __restrict__ query_start,
+                                    const int* __restrict__ slots, int heads, int elements, int seg_len, int segs) {
+    const int request = blockIdx.x, head = blockIdx.y;
+    const int length = query_start[request + 1] - query_start[request];
+    if (length <= 0) return;
+    const int used = (length + seg_len - 1) / seg_len;
+    for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < elements; e += gridDim.z * blockDim.x) {
+        float carried = 0.0f;
+        for (int s = 0; s < used; ++s) {
+            const size_t at = ((size_t)request * segs + s) * heads + head;
+            float* cell = seg_state + at * elements + e;
+            const float ended = *cell;
+            if (s > 0) {
+                *cell = carried;                                    // what the second pass starts from
+                carried = fmaf(seg_decay[at], carried, ended);
+            } else {
+                carried = ended;
+            }
+        }
+        state[((size_t)slots[request] * heads + head) * elements + e] = carried;
     }
 }
 
@@ -202,9 +273,18 @@ int launch_recurrence_rows(const ScanParams& p, int requests, cudaStream_t strea
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("recurrence", cudaGetErrorString(status));
     }
-    dim3 grid(requests, p.heads, (p.dv + COLS - 1) / COLS);
+    dim3 grid(requests * (p.mode == 0 ? 1 : p.segs), p.heads, (p.dv + COLS - 1) / COLS);
     kernel<<<grid, kScanThreads, smem, stream>>>(p);
-    return check_launch("recurrence");
+    if (int status = check_launch("recurrence")) return status;
+    if (p.mode != 1) return 0;
+    const int elements = p.n * p.dv;
+    carry_states_kernel<<<dim3(requests, p.heads, min((elements + 255) / 256, 64)), 256, 0, stream>>>(
+        p.seg_state, p.seg_decay, p.state, p.query_start, p.slots, p.heads, elements, p.seg_len, p.segs);
+    if (int status = check_launch("carry_states")) return status;
+    ScanParams again = p;
+    again.mode = 2;
+    kernel<<<grid, kScanThreads, smem, stream>>>(again);
+    return check_launch("recurrence (second pass)");
 }
 
 template <typename T, bool SSD>
@@ -216,7 +296,8 @@ int launch_recurrence(const ScanParams& p, int requests, cudaStream_t stream) {
     // keeps four rows at least (64 rows of state for 16 columns, 128 for 8).
     const long long sms = sm_count() > 0 ? sm_count() : 1;
     int cols = 32;
-    while (cols > 8 && (long long)requests * p.heads * ((p.dv + cols - 1) / cols) < sms && p.n > 32 * (32 / cols)) cols /= 2;
+    const long long rows_of_blocks = (long long)requests * (p.mode == 0 ? 1 : p.segs);
+    while (cols > 8 && rows_of_blocks * p.heads * ((p.dv + cols - 1) / cols) < sms && p.n > 32 * (32 / cols)) cols /= 2;
 #define B200_ROWS(NPT, COLS) return launch_recurrence_rows<T, NPT, COLS, SSD>(p, requests, stream)
     if (cols == 32) {
         if (p.n <= 32) B200_ROWS(4, 32);
@@ -232,6 +313,17 @@ int launch_recurrence(const ScanParams& p, int requests, cudaStream_t stream) {
     if (p.n <= 128) B200_ROWS(4, 8);
     B200_ROWS(8, 8);
 #undef B200_ROWS
+}
+
+// segs <= 1: every request's tokens in one chain.  Otherwise seg_state holds [requests * segs, heads, n, dv]
+// floats and seg_decay [requests * segs, heads], and segs * seg_len covers the longest portion.
+inline int set_segments(ScanParams& p, int seg_len, int segs, float* seg_state, float* seg_decay) {
+    p.mode = 0; p.seg_len = 0; p.segs = 1; p.seg_state = nullptr; p.seg_decay = nullptr;
+    if (segs <= 1) return 0;
+    if (seg_len <= 0 || seg_state == nullptr || seg_decay == nullptr)
+        return fail("recurrence", "segments need a length and scratch for their states and decays");
+    p.mode = 1; p.seg_len = seg_len; p.segs = segs; p.seg_state = seg_state; p.seg_decay = seg_decay;
+    return 0;
 }
 
 // out[t, c] = silu(bias[c] + sum_i w[i, c] * in[t - (taps - 1 - i), c]) within one request (the taps'
@@ -328,12 +420,15 @@ __global__ void conv_state_kernel(const T* __restrict__ in, int stride, int offs
 
 }  // namespace b200
 
+B200_EXPORT int b200_recurrence_sm_count() { return b200::sm_count(); }
+
 // Decayed linear attention over the packed projection `proj` [T, stride] = [.. q .. k .. v ..] (columns
 // off_q, off_k, off_v; q and k are heads x n, v heads x dv; silu is applied on load).  y: float32
 // [T, heads * dv].  state: float32 [slots + 1, heads, n, dv].  dtype of proj: 0 float32, 1 bfloat16.
 B200_EXPORT int b200_decayed_linear_attention(const void* proj, int stride, int off_q, int off_k, int off_v,
                                               const float* decay, const int* query_start, const int* slots,
                                               float* state, float* y, int requests, int heads, int n, int dv,
+                                              int seg_len, int segs, float* seg_state, float* seg_decay,
                                               int dtype, cudaStream_t stream) {
     using namespace b200;
     if (requests == 0) return 0;
@@ -341,6 +436,7 @@ B200_EXPORT int b200_decayed_linear_attention(const void* proj, int stride, int 
     p.query_start = query_start; p.slots = slots; p.state = state; p.y = y;
     p.heads = heads; p.n = n; p.dv = dv;
     p.proj = proj; p.stride = stride; p.off_q = off_q; p.off_k = off_k; p.off_v = off_v; p.decay = decay;
+    if (int status = set_segments(p, seg_len, segs, seg_state, seg_decay)) return status;
     if (dtype == 0) return launch_recurrence<float, false>(p, requests, stream);
     if (dtype == 1) return launch_recurrence<__nv_bfloat16, false>(p, requests, stream);
     return fail("decayed_linear_attention", "dtype must be 0 (float32) or 1 (bfloat16)");
@@ -352,8 +448,8 @@ B200_EXPORT int b200_decayed_linear_attention(const void* proj, int stride, int 
 B200_EXPORT int b200_selective_scan(const float* xbc, int xbc_width, const void* proj, int stride, int off_dt,
                                     const float* dt_bias, const float* a_log, const float* skip,
                                     const int* query_start, const int* slots, float* state, float* y,
-                                    int requests, int heads, int groups, int n, int dv, int dtype,
-                                    cudaStream_t stream) {
+                                    int requests, int heads, int groups, int n, int dv, int seg_len, int segs,
+                                    float* seg_state, float* seg_decay, int dtype, cudaStream_t stream) {
     using namespace b200;
     if (requests == 0) return 0;
     if (groups <= 0 || heads % groups) return fail("selective_scan", "heads must be a multiple of groups");
@@ -364,6 +460,7 @@ B200_EXPORT int b200_selective_scan(const float* xbc, int xbc_width, const void*
     p.xbc = xbc; p.xbc_width = xbc_width; p.off_b = heads * dv; p.off_c = heads * dv + groups * n;
     p.group_heads = heads / groups;
     p.dt_bias = dt_bias; p.a_log = a_log; p.skip = skip;
+    if (int status = set_segments(p, seg_len, segs, seg_state, seg_decay)) return status;
     if (dtype == 0) return launch_recurrence<float, true>(p, requests, stream);
     if (dtype == 1) return launch_recurrence<__nv_bfloat16, true>(p, requests, stream);
     return fail("selective_scan", "dtype must be 0 (float32) or 1 (bfloat16)");

@@ -116,7 +116,7 @@ def head_norm_scale_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: tor
 
 # Tests set this to False to drive the float32-arithmetic kernel through the same call.
 USE_TENSOR_CORES = True
-_sms: dict[int, int] = {}
+_sms: dict = {}
 
 
 def _sm_count() -> int:
@@ -187,15 +187,57 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
 
 
 # ------------------------------------------------------------------ recurrences
+# A portion of at least twice this many tokens is cut into segments of about this length that run
+# side by side (see csrc/recurrence.cu); tests lower it to cut short sequences too.
+SCAN_SEGMENT = 256
+SCAN_SCRATCH_BYTES = 256 << 20      # the most that the segments' states may take
+
+
+def _recurrence_sms() -> int:
+    device = torch.cuda.current_device()
+    if ("recurrence", device) not in _sms:
+        from ..csrc.build import load_library
+        _sms[("recurrence", device)] = int(load_library("recurrence").b200_recurrence_sm_count()) or 1
+    return _sms[("recurrence", device)]
+
+
+def _segments(max_query_len: int | None, requests: int, heads: int, rows: int, columns: int, device
+              ) -> tuple[int, int, torch.Tensor | None, torch.Tensor | None]:
+    """``(seg_len, segs, states, decays)`` for a step whose longest portion has ``max_query_len`` tokens;
+    ``segs`` is 1 (and nothing is allocated) where the portions are short or the scratch would be too large."""
+    if max_query_len is None or max_query_len < 2 * SCAN_SEGMENT:
+        return 0, 1, None, None
+    # Segments cost half as much work again (the second pass).  They pay where the launch would leave
+    # most SMs without a block (a linear-attention layer of 8 heads: 385 against 194 us for 2048 tokens);
+    # a launch that fills half of the GPU already is bound by its arithmetic and would only lose.
+    if 2 * requests * heads * -(-columns // 32) > _recurrence_sms():
+        return 0, 1, None, None
+    per_segment = requests * heads * rows * columns * 4
+    segs = min(-(-max_query_len // SCAN_SEGMENT), SCAN_SCRATCH_BYTES // max(1, per_segment))
+    if segs < 2:
+        return 0, 1, None, None
+    seg_len = -(-max_query_len // segs)
+    seg_len = -(-seg_len // 16) * 16                    # whole tiles of the kernel
+    segs = -(-max_query_len // seg_len)
+    states = torch.empty((requests * segs, heads, rows, columns), dtype=torch.float32, device=device)
+    decays = torch.empty((requests * segs, heads), dtype=torch.float32, device=device)
+    return seg_len, segs, states, decays
+
+
 def decayed_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], decay: torch.Tensor,
                              query_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
-                             y: torch.Tensor, heads: int, key_dim: int, value_dim: int) -> None:
+                             y: torch.Tensor, heads: int, key_dim: int, value_dim: int,
+                             max_query_len: int | None = None) -> None:
     """Per request and head, token after token: ``S <- decay_h S + k v^T``, ``y = S^T q`` with q, k
     (``heads x key_dim``) and v (``heads x value_dim``) = silu of the columns of ``proj`` that start
     at ``offsets = (q, k, v)``.  ``state``: float32 ``[slots + 1, heads, key_dim, value_dim]``, read
-    at the request's slot and left advanced; ``y``: float32 ``[T, heads * value_dim]``."""
+    at the request's slot and left advanced; ``y``: float32 ``[T, heads * value_dim]``.  With
+    ``max_query_len`` (the longest portion of the step) long portions run in segments side by side."""
     tokens, stride = proj.shape
     requests = slots.shape[0]
+    seg_len, segs, seg_state, seg_decay = _segments(max_query_len, requests, heads, key_dim, value_dim, proj.device)
+    if segs > 1:
+        count_launch(2)
     _run("recurrence", "b200_decayed_linear_attention",
          _P(_check("projection", proj, _RUN)), _I(stride), _I(offsets[0]), _I(offsets[1]), _I(offsets[2]),
          _P(_check("decay", decay, torch.float32, (heads,))),
@@ -203,13 +245,15 @@ def decayed_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], 
          _P(_check("state slots", slots, torch.int32, (requests,))),
          _P(_check("state", state, torch.float32, (None, heads, key_dim, value_dim))),
          _P(_check("recurrence output", y, torch.float32, (tokens, heads * value_dim))),
-         _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(_code(proj.dtype)), _stream())
+         _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(seg_len), _I(segs),
+         _P(seg_state.data_ptr() if segs > 1 else 0), _P(seg_decay.data_ptr() if segs > 1 else 0),
+         _I(_code(proj.dtype)), _stream())
 
 
 def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bias: torch.Tensor,
                    a_log: torch.Tensor, skip: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
                    state: torch.Tensor, y: torch.Tensor, heads: int, groups: int, state_dim: int,
-                   value_dim: int) -> None:
+                   value_dim: int, max_query_len: int | None = None) -> None:
     """Per request and head, token after token, with ``dt = softplus(proj[t, dt_offset + h] +
     dt_bias[h])``: ``S <- exp(-exp(a_log_h) dt) S + dt B x^T``, ``y = S^T C + skip_h x``; x, B and C are
     the columns ``[heads * value_dim | groups * state_dim | groups * state_dim]`` of the float32
@@ -217,6 +261,9 @@ def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bia
     tokens = xbc.shape[0]
     requests = slots.shape[0]
     width = heads * value_dim + 2 * groups * state_dim
+    seg_len, segs, seg_state, seg_decay = _segments(max_query_len, requests, heads, state_dim, value_dim, xbc.device)
+    if segs > 1:
+        count_launch(2)
     _run("recurrence", "b200_selective_scan",
          _P(_check("convolved inputs", xbc, torch.float32, (tokens, width))), _I(width),
          _P(_check("projection", proj, _RUN, (tokens, None))), _I(proj.shape[1]), _I(dt_offset),
@@ -226,7 +273,9 @@ def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bia
          _P(_check("state slots", slots, torch.int32, (requests,))),
          _P(_check("state", state, torch.float32, (None, heads, state_dim, value_dim))),
          _P(_check("recurrence output", y, torch.float32, (tokens, heads * value_dim))),
-         _I(requests), _I(heads), _I(groups), _I(state_dim), _I(value_dim), _I(_code(proj.dtype)), _stream())
+         _I(requests), _I(heads), _I(groups), _I(state_dim), _I(value_dim), _I(seg_len), _I(segs),
+         _P(seg_state.data_ptr() if segs > 1 else 0), _P(seg_decay.data_ptr() if segs > 1 else 0),
+         _I(_code(proj.dtype)), _stream())
 
 
 def causal_conv_silu(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor,

@@ -80,7 +80,7 @@ class DecayedLinearAttention(Mixer):
         y = torch.empty((tokens, self.inner), dtype=torch.float32, device=x.device)
         kernels.decayed_linear_attention(proj, (self.inner, self.inner + keys, self.inner + 2 * keys), self.decay,
                                          ctx.query_start, ctx.state_slots, state, y, self.num_heads, self.head_dim,
-                                         self.value_dim)
+                                         self.value_dim, ctx.max_query_len)
         gated = torch.empty((tokens, self.inner), dtype=x.dtype, device=x.device)
         kernels.gated_group_norm(y, proj, self.norm, gated, 1, False, self.norm_eps)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
@@ -153,7 +153,7 @@ class SelectiveScan(Mixer):
         y = torch.empty((tokens, self.inner), dtype=torch.float32, device=x.device)
         kernels.selective_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.a_log, self.skip,
                                ctx.query_start, ctx.state_slots, cache.states["state"], y, self.num_heads,
-                               self.groups, self.state_dim, self.value_dim)
+                               self.groups, self.state_dim, self.value_dim, ctx.max_query_len)
         gated = torch.empty((tokens, self.inner), dtype=x.dtype, device=x.device)
         kernels.gated_group_norm(y, proj, self.norm, gated, self.norm_groups, True, self.norm_eps)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
