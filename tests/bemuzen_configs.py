@@ -60,10 +60,25 @@ BZ_D = {
     ],
 }
 
-CONFIGS = {"A": (BZ_A, 16), "B": (BZ_B, 8), "C": (BZ_C, 32), "D": (BZ_D, 16)}
+# Odd sizes: a width, head sizes and feed-forward widths that are no multiple of four (the kernels' forms
+# of one element a thread, the library's products over odd rows), a convolution of one tap (no inputs to
+# keep), as many groups as heads, a temperature that steps at every position, large hash constants.
+BZ_E = {
+    "architecture": "Bemuzen", "vocab": 61, "width": 50, "logit_scale": 2.0, "norm": {"eps": 1e-4},
+    "embedding": {"bigram": {"buckets": 17, "mul_prev": 1000003, "mul_cur": 998244353}},
+    "layers": [
+        _mamba({"heads": 3, "vdim": 7, "state": 5, "groups": 3, "conv": 1, "norm_groups": 1}, 77),
+        _parallel({"heads": 3, "kv_heads": 3, "dim": 10, "vdim": 6, "scale": 0.5, "q_temp": {"coef": 0.2, "every": 1}},
+                  {"heads": 1, "dim": 6, "vdim": 9, "decay": [1.0]}, 33),
+        _mamba({"heads": 2, "vdim": 9, "state": 33, "groups": 1, "conv": 5, "norm_groups": 3}, None),
+    ],
+}
+
+CONFIGS = {"A": (BZ_A, 16), "B": (BZ_B, 8), "C": (BZ_C, 32), "D": (BZ_D, 16), "E": (BZ_E, 4)}
 LENGTHS = {
     "A": {"a": 70, "b": 45, "c": 100, "d": 37, "e": 64, "f": 1, "g": 150},
     "B": {"a": 70, "b": 33, "c": 90, "d": 2, "e": 64, "g": 130},
     "C": {"a": 70, "b": 45, "c": 3, "d": 37, "g": 110},
     "D": {"a": 70, "b": 45, "c": 130, "d": 1, "g": 200},
+    "E": {"a": 41, "b": 2, "c": 23, "g": 70},
 }
