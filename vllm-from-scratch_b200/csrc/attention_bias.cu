@@ -25,6 +25,8 @@ __global__ void head_norm_scale_cache_kernel(
     const float* __restrict__ q_weight, const float* __restrict__ k_weight, T* __restrict__ q_out,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int d, int dv, int page_size, float eps,
     float temp_coef, int temp_every) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     const int token = blockIdx.x;
     const int warps = blockDim.x >> 5;
     const int head_slot = blockIdx.y * warps + (threadIdx.x >> 5);
@@ -81,6 +83,8 @@ __global__ void __launch_bounds__(kWarps * 32) biased_paged_attention_kernel(
     T* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, const float* __restrict__ slopes, int num_requests, int max_pages,
     int nq, int nkv, int d, int dv, int page_size, float scale, int window) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     extern __shared__ float smem[];
     float* q_s = smem;                                   // [16][d]
     float* k_s = q_s + kQueryTile * d;                   // [32][d + 1]
@@ -215,7 +219,7 @@ int launch_biased(const void* q, const void* k_pages, const void* v_pages, void*
         if (status != cudaSuccess) return fail("biased_paged_attention", cudaGetErrorString(status));
     }
     dim3 grid(num_tokens / kQueryTile + num_requests, nq);
-    kernel<<<grid, kWarps * 32, smem, stream>>>(
+    launch_overlapped_if(num_tokens <= kOverlapMostRows, kernel, grid, kWarps * 32, smem, stream,
         (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, query_start, seq_lens, block_table, slopes,
         num_requests, max_pages, nq, nkv, d, dv, page_size, scale, window);
     return check_launch("biased_paged_attention");
@@ -254,11 +258,11 @@ B200_EXPORT int b200_head_norm_scale_cache(
     dim3 grid(num_tokens, (nq + 2 * nkv + warps - 1) / warps);
     if (grid.y > 65535) return fail("head_norm_scale_cache", "too many heads");
     if (dtype == 0)
-        head_norm_scale_cache_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, head_norm_scale_cache_kernel<float>, grid, warps * 32, 0, stream,
             (const float*)qkv, positions, slots, q_weight, k_weight, (float*)q_out, (float*)k_pages, (float*)v_pages,
             nq, nkv, d, dv, page_size, eps, temp_coef, temp_every);
     else if (dtype == 1)
-        head_norm_scale_cache_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, head_norm_scale_cache_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream,
             (const __nv_bfloat16*)qkv, positions, slots, q_weight, k_weight, (__nv_bfloat16*)q_out,
             (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, nq, nkv, d, dv, page_size, eps, temp_coef, temp_every);
     else

@@ -126,6 +126,27 @@ inline void launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, 
     cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
+// The same, but overlapped only where `allowed`: a launch of many blocks gains nothing from being
+// scheduled early, and its waiting blocks would take room from the kernel ahead.
+template <typename... Params, typename... Args>
+inline void launch_overlapped_if(bool allowed, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = (allowed && overlap_enabled()) ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// Steps of few tokens are chains of short kernels, where the overlap pays.
+constexpr int kOverlapMostRows = 64;
+
 }  // namespace b200
 
 // One translation unit per shared object, so this definition appears once in each.

@@ -18,6 +18,8 @@ template <typename T>
 __global__ void add_normed_rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ x_weight, float x_eps,
                                           float* __restrict__ residual, const float* __restrict__ weight,
                                           T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
     const int out_row = blockIdx.x;
     const int row = rows ? rows[out_row] : out_row;
@@ -49,6 +51,8 @@ template <typename T>
 __global__ void paired_norm_mean_kernel(const T* __restrict__ a, const float* __restrict__ wa,
                                         const T* __restrict__ b, const float* __restrict__ wb,
                                         T* __restrict__ out, int hidden, float eps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * hidden;
     float sum_a = 0.0f, sum_b = 0.0f;
@@ -91,6 +95,8 @@ template <typename T>
 __global__ void add_normed_rmsnorm_vec_kernel(const T* __restrict__ x, const float* __restrict__ x_weight, float x_eps,
                                               float* __restrict__ residual, const float* __restrict__ weight,
                                               T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
     const int out_row = blockIdx.x;
     const int row = rows ? rows[out_row] : out_row;
@@ -156,6 +162,8 @@ template <typename T>
 __global__ void paired_norm_mean_vec_kernel(const T* __restrict__ a, const float* __restrict__ wa,
                                             const T* __restrict__ b, const float* __restrict__ wb,
                                             T* __restrict__ out, int hidden, float eps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[66];
     const size_t base = (size_t)blockIdx.x * hidden;
     float4 av[kRowSteps], bv[kRowSteps];
@@ -190,6 +198,8 @@ template <typename T, bool GATE_FIRST>
 __global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
                                             const float* __restrict__ weight, T* __restrict__ out, int width,
                                             int group_width, float eps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
     const size_t token = blockIdx.x;
     const int first = blockIdx.y * group_width;
@@ -240,6 +250,8 @@ template <typename T, bool GATE_FIRST>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
                                         const float* __restrict__ weight, T* __restrict__ out, int width,
                                         int group_width, float eps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
     const size_t token = blockIdx.x;
     const int first = blockIdx.y * group_width;
@@ -275,6 +287,8 @@ __global__ void bigram_embedding_kernel(const T* __restrict__ table, const T* __
                                         const int* __restrict__ slots, int* __restrict__ previous,
                                         float* __restrict__ residual, int hidden, int vocab, int buckets,
                                         int mul_prev, int mul_cur, int* __restrict__ error_flag) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ int before_s;
     const int token = blockIdx.x;
     const int id = ids[token];
@@ -327,19 +341,19 @@ B200_EXPORT int b200_add_normed_rmsnorm(const void* x, const float* x_weight, fl
     if (hidden % 4 == 0 && (addresses & 15) == 0 && vec_threads(hidden) > 0 && (dtype == 0 || dtype == 1)) {
         const int threads = vec_threads(hidden);
         if (dtype == 0)
-            add_normed_rmsnorm_vec_kernel<float><<<num_rows, threads, 0, stream>>>(
+            launch_overlapped_if(num_rows <= kOverlapMostRows, add_normed_rmsnorm_vec_kernel<float>, num_rows, threads, 0, stream,
                 (const float*)x, x_weight, x_eps, residual, weight, (float*)out, rows, hidden, eps);
         else
-            add_normed_rmsnorm_vec_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+            launch_overlapped_if(num_rows <= kOverlapMostRows, add_normed_rmsnorm_vec_kernel<__nv_bfloat16>, num_rows, threads, 0, stream,
                 (const __nv_bfloat16*)x, x_weight, x_eps, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
         return check_launch("add_normed_rmsnorm");
     }
     const int threads = row_threads(hidden);
     if (dtype == 0)
-        add_normed_rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>(
+        launch_overlapped_if(num_rows <= kOverlapMostRows, add_normed_rmsnorm_kernel<float>, num_rows, threads, 0, stream,
             (const float*)x, x_weight, x_eps, residual, weight, (float*)out, rows, hidden, eps);
     else if (dtype == 1)
-        add_normed_rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+        launch_overlapped_if(num_rows <= kOverlapMostRows, add_normed_rmsnorm_kernel<__nv_bfloat16>, num_rows, threads, 0, stream,
             (const __nv_bfloat16*)x, x_weight, x_eps, residual, weight, (__nv_bfloat16*)out, rows, hidden, eps);
     else
         return fail("add_normed_rmsnorm", "dtype must be 0 (float32) or 1 (bfloat16)");
@@ -355,19 +369,19 @@ B200_EXPORT int b200_paired_norm_mean(const void* a, const float* wa, const void
     if (hidden % 4 == 0 && (addresses & 15) == 0 && vec_threads(hidden) > 0 && (dtype == 0 || dtype == 1)) {
         const int threads = vec_threads(hidden);
         if (dtype == 0)
-            paired_norm_mean_vec_kernel<float><<<num_rows, threads, 0, stream>>>(
+            launch_overlapped_if(num_rows <= kOverlapMostRows, paired_norm_mean_vec_kernel<float>, num_rows, threads, 0, stream,
                 (const float*)a, wa, (const float*)b, wb, (float*)out, hidden, eps);
         else
-            paired_norm_mean_vec_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+            launch_overlapped_if(num_rows <= kOverlapMostRows, paired_norm_mean_vec_kernel<__nv_bfloat16>, num_rows, threads, 0, stream,
                 (const __nv_bfloat16*)a, wa, (const __nv_bfloat16*)b, wb, (__nv_bfloat16*)out, hidden, eps);
         return check_launch("paired_norm_mean");
     }
     const int threads = row_threads(hidden);
     if (dtype == 0)
-        paired_norm_mean_kernel<float><<<num_rows, threads, 0, stream>>>(
+        launch_overlapped_if(num_rows <= kOverlapMostRows, paired_norm_mean_kernel<float>, num_rows, threads, 0, stream,
             (const float*)a, wa, (const float*)b, wb, (float*)out, hidden, eps);
     else if (dtype == 1)
-        paired_norm_mean_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+        launch_overlapped_if(num_rows <= kOverlapMostRows, paired_norm_mean_kernel<__nv_bfloat16>, num_rows, threads, 0, stream,
             (const __nv_bfloat16*)a, wa, (const __nv_bfloat16*)b, wb, (__nv_bfloat16*)out, hidden, eps);
     else
         return fail("paired_norm_mean", "dtype must be 0 (float32) or 1 (bfloat16)");
@@ -390,7 +404,7 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
         (dtype == 0 || dtype == 1)) {
         const int threads = vec_threads(group_width);
 #define B200_VEC(T, FIRST)                                                                                      \
-        gated_group_norm_vec_kernel<T, FIRST><<<grid, threads, 0, stream>>>(y, (const T*)gate, gate_stride, weight, \
+        launch_overlapped_if(tokens <= kOverlapMostRows, gated_group_norm_vec_kernel<T, FIRST>, grid, threads, 0, stream, y, (const T*)gate, gate_stride, weight, \
                                                                             (T*)out, width, group_width, eps)
         if (dtype == 0 && gate_first) B200_VEC(float, true);
         else if (dtype == 0) B200_VEC(float, false);
@@ -401,7 +415,7 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
     }
     const int threads = row_threads(group_width);
 #define B200_CASE(T, FIRST)                                                                             \
-    gated_group_norm_kernel<T, FIRST><<<grid, threads, 0, stream>>>(y, (const T*)gate, gate_stride, weight, \
+    launch_overlapped_if(tokens <= kOverlapMostRows, gated_group_norm_kernel<T, FIRST>, grid, threads, 0, stream, y, (const T*)gate, gate_stride, weight, \
                                                                     (T*)out, width, group_width, eps)
     if (dtype == 0 && gate_first) B200_CASE(float, true);
     else if (dtype == 0) B200_CASE(float, false);
@@ -422,11 +436,11 @@ B200_EXPORT int b200_bigram_embedding(const void* table, const void* bigram, con
     if (buckets <= 0) return fail("bigram_embedding", "buckets must be positive");
     const int threads = row_threads(hidden);
     if (dtype == 0)
-        bigram_embedding_kernel<float><<<num_tokens, threads, 0, stream>>>(
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, bigram_embedding_kernel<float>, num_tokens, threads, 0, stream,
             (const float*)table, (const float*)bigram, ids, positions, token_request, query_start, slots, previous,
             residual, hidden, vocab, buckets, mul_prev, mul_cur, error_flag);
     else if (dtype == 1)
-        bigram_embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, bigram_embedding_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream,
             (const __nv_bfloat16*)table, (const __nv_bfloat16*)bigram, ids, positions, token_request, query_start,
             slots, previous, residual, hidden, vocab, buckets, mul_prev, mul_cur, error_flag);
     else

@@ -59,6 +59,7 @@ struct ScanParams {
     // A long portion in segments (mode 1 and 2, see below): tokens per segment, segments a request at
     // most, the segments' states [R * segs, H, N, dv] and decays [R * segs, H].
     int mode, seg_len, segs;
+    int tokens;                 // of the whole step (a step of few tokens is launched overlapped)
     float* seg_state;
     float* seg_decay;
 };
@@ -67,6 +68,8 @@ struct ScanParams {
 // (zeros in k and q there).
 template <typename T, int NPT, int COLS, bool SSD>
 __global__ void __launch_bounds__(kScanThreads) recurrence_kernel(ScanParams p) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     extern __shared__ __align__(16) float scan_smem[];
     constexpr int kScanColumns = COLS, kScanParts = kScanThreads / COLS;
     constexpr int kRows = NPT * kScanParts;
@@ -242,6 +245,8 @@ __global__ void __launch_bounds__(kScanThreads) recurrence_kernel(ScanParams p) 
 __global__ void carry_states_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_decay,
                                     float* __restrict__ state, const int* __restrict__ query_start,
                                     const int* __restrict__ slots, int heads, int elements, int seg_len, int segs) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     const int request = blockIdx.x, head = blockIdx.y;
     const int length = query_start[request + 1] - query_start[request];
     if (length <= 0) return;
@@ -274,16 +279,16 @@ int launch_recurrence_rows(const ScanParams& p, int requests, cudaStream_t strea
         if (status != cudaSuccess) return fail("recurrence", cudaGetErrorString(status));
     }
     dim3 grid(requests * (p.mode == 0 ? 1 : p.segs), p.heads, (p.dv + COLS - 1) / COLS);
-    kernel<<<grid, kScanThreads, smem, stream>>>(p);
+    launch_overlapped_if(p.tokens <= kOverlapMostRows, kernel, grid, kScanThreads, smem, stream, p);
     if (int status = check_launch("recurrence")) return status;
     if (p.mode != 1) return 0;
     const int elements = p.n * p.dv;
-    carry_states_kernel<<<dim3(requests, p.heads, min((elements + 255) / 256, 64)), 256, 0, stream>>>(
+    launch_overlapped_if(false, carry_states_kernel, dim3(requests, p.heads, min((elements + 255) / 256, 64)), 256, 0, stream,
         p.seg_state, p.seg_decay, p.state, p.query_start, p.slots, p.heads, elements, p.seg_len, p.segs);
     if (int status = check_launch("carry_states")) return status;
     ScanParams again = p;
     again.mode = 2;
-    kernel<<<grid, kScanThreads, smem, stream>>>(again);
+    launch_overlapped_if(false, kernel, grid, kScanThreads, smem, stream, again);
     return check_launch("recurrence (second pass)");
 }
 
@@ -335,6 +340,8 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int stride, in
                                         const float* __restrict__ bias, const float* __restrict__ state,
                                         const int* __restrict__ token_request, const int* __restrict__ query_start,
                                         const int* __restrict__ slots, float* __restrict__ out, int channels, int taps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     const int token = blockIdx.x;
     const int request = token_request[token];
     const int place = token - query_start[request];        // index within this step's portion
@@ -358,6 +365,8 @@ __global__ void causal_conv_silu_vec_kernel(const T* __restrict__ in, int stride
                                             const float* __restrict__ bias, const float* __restrict__ state,
                                             const int* __restrict__ token_request, const int* __restrict__ query_start,
                                             const int* __restrict__ slots, float* __restrict__ out, int channels, int taps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     const int token = blockIdx.x;
     const int request = token_request[token];
     const int place = token - query_start[request];
@@ -397,6 +406,8 @@ template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ in, int stride, int offset, float* __restrict__ state,
                                   const int* __restrict__ query_start, const int* __restrict__ slots, int channels,
                                   int taps) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     constexpr int kMost = 15;
     const int request = blockIdx.x;
     const int begin = query_start[request], length = query_start[request + 1] - begin;
@@ -427,14 +438,14 @@ B200_EXPORT int b200_recurrence_sm_count() { return b200::sm_count(); }
 // [T, heads * dv].  state: float32 [slots + 1, heads, n, dv].  dtype of proj: 0 float32, 1 bfloat16.
 B200_EXPORT int b200_decayed_linear_attention(const void* proj, int stride, int off_q, int off_k, int off_v,
                                               const float* decay, const int* query_start, const int* slots,
-                                              float* state, float* y, int requests, int heads, int n, int dv,
-                                              int seg_len, int segs, float* seg_state, float* seg_decay,
+                                              float* state, float* y, int tokens, int requests, int heads, int n,
+                                              int dv, int seg_len, int segs, float* seg_state, float* seg_decay,
                                               int dtype, cudaStream_t stream) {
     using namespace b200;
     if (requests == 0) return 0;
     ScanParams p = {};
     p.query_start = query_start; p.slots = slots; p.state = state; p.y = y;
-    p.heads = heads; p.n = n; p.dv = dv;
+    p.heads = heads; p.n = n; p.dv = dv; p.tokens = tokens;
     p.proj = proj; p.stride = stride; p.off_q = off_q; p.off_k = off_k; p.off_v = off_v; p.decay = decay;
     if (int status = set_segments(p, seg_len, segs, seg_state, seg_decay)) return status;
     if (dtype == 0) return launch_recurrence<float, false>(p, requests, stream);
@@ -448,14 +459,14 @@ B200_EXPORT int b200_decayed_linear_attention(const void* proj, int stride, int 
 B200_EXPORT int b200_selective_scan(const float* xbc, int xbc_width, const void* proj, int stride, int off_dt,
                                     const float* dt_bias, const float* a_log, const float* skip,
                                     const int* query_start, const int* slots, float* state, float* y,
-                                    int requests, int heads, int groups, int n, int dv, int seg_len, int segs,
+                                    int tokens, int requests, int heads, int groups, int n, int dv, int seg_len, int segs,
                                     float* seg_state, float* seg_decay, int dtype, cudaStream_t stream) {
     using namespace b200;
     if (requests == 0) return 0;
     if (groups <= 0 || heads % groups) return fail("selective_scan", "heads must be a multiple of groups");
     ScanParams p = {};
     p.query_start = query_start; p.slots = slots; p.state = state; p.y = y;
-    p.heads = heads; p.n = n; p.dv = dv;
+    p.heads = heads; p.n = n; p.dv = dv; p.tokens = tokens;
     p.proj = proj; p.stride = stride; p.off_dt = off_dt;
     p.xbc = xbc; p.xbc_width = xbc_width; p.off_b = heads * dv; p.off_c = heads * dv + groups * n;
     p.group_heads = heads / groups;
@@ -487,24 +498,24 @@ B200_EXPORT int b200_causal_conv_silu(const void* in, int stride, int offset, co
         const int sms = sm_count() > 0 ? sm_count() : 1;
         const int wide = max(1, min(most, (2 * sms + tokens - 1) / tokens));
         if (dtype == 0)
-            causal_conv_silu_vec_kernel<float><<<dim3(tokens, wide), 2 * threads, 0, stream>>>(
+            launch_overlapped_if(tokens <= kOverlapMostRows, causal_conv_silu_vec_kernel<float>, dim3(tokens, wide), 2 * threads, 0, stream,
                 (const float*)in, stride, offset, w, bias, state, token_request, query_start, slots, out, channels, taps);
         else
-            causal_conv_silu_vec_kernel<__nv_bfloat16><<<dim3(tokens, wide), 2 * threads, 0, stream>>>(
+            launch_overlapped_if(tokens <= kOverlapMostRows, causal_conv_silu_vec_kernel<__nv_bfloat16>, dim3(tokens, wide), 2 * threads, 0, stream,
                 (const __nv_bfloat16*)in, stride, offset, w, bias, state, token_request, query_start, slots, out, channels, taps);
     } else if (dtype == 0)
-        causal_conv_silu_kernel<float><<<dim3(tokens, tiles), threads, 0, stream>>>(
+        launch_overlapped_if(tokens <= kOverlapMostRows, causal_conv_silu_kernel<float>, dim3(tokens, tiles), threads, 0, stream,
             (const float*)in, stride, offset, w, bias, state, token_request, query_start, slots, out, channels, taps);
     else
-        causal_conv_silu_kernel<__nv_bfloat16><<<dim3(tokens, tiles), threads, 0, stream>>>(
+        launch_overlapped_if(tokens <= kOverlapMostRows, causal_conv_silu_kernel<__nv_bfloat16>, dim3(tokens, tiles), threads, 0, stream,
             (const __nv_bfloat16*)in, stride, offset, w, bias, state, token_request, query_start, slots, out, channels, taps);
     if (int status = check_launch("causal_conv_silu")) return status;
     if (taps == 1) return 0;
     if (dtype == 0)
-        conv_state_kernel<float><<<dim3(requests, tiles), threads, 0, stream>>>(
+        launch_overlapped_if(tokens <= kOverlapMostRows, conv_state_kernel<float>, dim3(requests, tiles), threads, 0, stream,
             (const float*)in, stride, offset, state, query_start, slots, channels, taps);
     else
-        conv_state_kernel<__nv_bfloat16><<<dim3(requests, tiles), threads, 0, stream>>>(
+        launch_overlapped_if(tokens <= kOverlapMostRows, conv_state_kernel<__nv_bfloat16>, dim3(requests, tiles), threads, 0, stream,
             (const __nv_bfloat16*)in, stride, offset, state, query_start, slots, channels, taps);
     return check_launch("conv_state");
 }

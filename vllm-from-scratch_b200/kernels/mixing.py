@@ -245,7 +245,7 @@ def decayed_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], 
          _P(_check("state slots", slots, torch.int32, (requests,))),
          _P(_check("state", state, torch.float32, (None, heads, key_dim, value_dim))),
          _P(_check("recurrence output", y, torch.float32, (tokens, heads * value_dim))),
-         _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(seg_len), _I(segs),
+         _I(tokens), _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(seg_len), _I(segs),
          _P(seg_state.data_ptr() if segs > 1 else 0), _P(seg_decay.data_ptr() if segs > 1 else 0),
          _I(_code(proj.dtype)), _stream())
 
@@ -273,7 +273,7 @@ def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bia
          _P(_check("state slots", slots, torch.int32, (requests,))),
          _P(_check("state", state, torch.float32, (None, heads, state_dim, value_dim))),
          _P(_check("recurrence output", y, torch.float32, (tokens, heads * value_dim))),
-         _I(requests), _I(heads), _I(groups), _I(state_dim), _I(value_dim), _I(seg_len), _I(segs),
+         _I(tokens), _I(requests), _I(heads), _I(groups), _I(state_dim), _I(value_dim), _I(seg_len), _I(segs),
          _P(seg_state.data_ptr() if segs > 1 else 0), _P(seg_decay.data_ptr() if segs > 1 else 0),
          _I(_code(proj.dtype)), _stream())
 
