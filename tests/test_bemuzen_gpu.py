@@ -295,7 +295,7 @@ def paged(tensor_rows, page_size, pages_order, heads, size, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(6, 2, 20, 36), (4, 2, 64, 64), (8, 1, 128, 128)])
+@pytest.mark.parametrize("shape", [(6, 2, 20, 36), (4, 2, 64, 64), (8, 1, 128, 128), (2, 1, 256, 256)])
 def test_biased_attention_far_keys_page_borders_and_temperature(dtype, shape):
     """Two requests that decode one token (one over 1500 keys, which the tensor-core kernel divides
     over several blocks) ahead of a request of 333 positions in scattered pages whose last 40 tokens
