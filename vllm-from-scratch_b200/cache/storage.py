@@ -31,6 +31,12 @@ class CacheGroup:
     value_slab: torch.Tensor | None = None
 
 
+def _value_dim(need: KVPagesNeed) -> int:
+    """Elements a position's values take per head: the keys' size unless told otherwise; 0 where the
+    cached rows serve as both."""
+    return need.head_dim if need.value_dim is None else need.value_dim
+
+
 def split_needs(need) -> tuple[KVPagesNeed | None, list[StateNeed]]:
     """What a part asked for (one need, a tuple of them or None) as its pages and its states."""
     items = [] if need is None else list(need) if isinstance(need, (tuple, list)) else [need]
@@ -64,7 +70,14 @@ class CacheStorage:
         for key, group in sorted(group_of_key.items(), key=lambda item: item[1]):
             need = KVPagesNeed(*key)
             count = len(members[group])
-            if need.value_dim is None:
+            if need.value_dim == 0:
+                # rows that serve as keys and as values: one slab, handed out under both names
+                keys = torch.zeros((count, num_pages, need.num_kv_heads, page_size, need.head_dim),
+                                   dtype=dtype, device=device)
+                self.groups.append(CacheGroup(need, members[group], keys))
+                for position, index in enumerate(members[group]):
+                    page_views[index] = (group, keys[position], keys[position])
+            elif need.value_dim is None:
                 slab = torch.zeros((count, 2, num_pages, need.num_kv_heads, page_size, need.head_dim),
                                    dtype=dtype, device=device)
                 self.groups.append(CacheGroup(need, members[group], slab))
@@ -121,7 +134,7 @@ class CacheStorage:
         group's pool has the same number of pages, so a page number exists once in each)."""
         element = torch.empty((), dtype=dtype).element_size()
         pages = [split_needs(need)[0] for need in needs]
-        return sum(need.num_kv_heads * page_size * (need.head_dim + (need.value_dim or need.head_dim)) * element
+        return sum(need.num_kv_heads * page_size * (need.head_dim + _value_dim(need)) * element
                    for need in pages if need is not None)
 
     @property
@@ -146,5 +159,5 @@ class CacheStorage:
 
     def bytes_per_token(self) -> int:
         """Cache bytes one position of one request occupies over all groups."""
-        return sum(len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + (g.need.value_dim or g.need.head_dim))
+        return sum(len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + _value_dim(g.need))
                    * g.slab.element_size() for g in self.groups)

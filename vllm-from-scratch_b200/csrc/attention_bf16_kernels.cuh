@@ -138,12 +138,24 @@ __device__ __forceinline__ void load_q_fragments(unsigned (&qa)[D / 16][4], cons
 // EXACT: the softmax weights stay float32 in the second product (three bfloat16 pieces each, see
 // split_bf16x3), and `slopes` (one per query head, or null) takes slope * (query position - key
 // position) off every score.
+// A sink: one more term exp(sink) in a row's softmax denominator that has no key and no value.
+// With the row's reference exponent m and sum l (both in units of log2 e) returns the factor that
+// the row's unnormalised output is to be multiplied by: 1 / (l + exp2(sink - m)), formed so that
+// neither term overflows.
+__device__ __forceinline__ float inverse_sum_with_sink(float m, float l, float sink_log2) {
+    if (m == -INFINITY) return 0.0f;
+    const float top = fmaxf(m, sink_log2);
+    const float keep = exp2f(m - top);
+    return keep / (l * keep + exp2f(sink_log2 - top));
+}
+
 template <int D, bool EXACT = false>
 __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
     const int* __restrict__ seq_lens, const int* __restrict__ block_table, int max_pages, int nq,
-    int nkv, int page_size, float scale_log2, int window, int splits, const float* __restrict__ slopes) {
+    int nkv, int page_size, float scale_log2, int window, int splits, const float* __restrict__ slopes,
+    const float* __restrict__ sinks) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);
     overlap_trigger();
@@ -307,7 +319,11 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
         }
         const size_t head = (size_t)request * nq + (size_t)kv_head * group + g;
         if (splits == 1) {
-            out[head * D + j] = __float2bfloat16_rn(l_sum > 0.0f ? acc / l_sum : 0.0f);
+            if (EXACT && sinks != nullptr)
+                out[head * D + j] = __float2bfloat16_rn(
+                    acc * inverse_sum_with_sink(m_star, l_sum, sinks[(size_t)kv_head * group + g] * kLog2e));
+            else
+                out[head * D + j] = __float2bfloat16_rn(l_sum > 0.0f ? acc / l_sum : 0.0f);
         } else {
             partial_o[(head * splits + split) * D + j] = acc;
             if (j == 0) {
@@ -322,10 +338,13 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
 // are fetched in one go (every load issued before any is used); more run through a loop.
 template <int D>
 __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                                    bf16* __restrict__ out, int splits) {
+                                    bf16* __restrict__ out, int splits, const float* __restrict__ sinks, int nq) {
     overlap_trigger();
     overlap_wait();
     const size_t head = blockIdx.x;
+    // A sink joins the sum once, here, where a row's splits meet.
+    const bool has_sink = sinks != nullptr;
+    const float sink_log2 = has_sink ? sinks[head % nq] * kLog2e : 0.0f;
     constexpr int kHeld = 16;
     if (splits <= kHeld) {
         for (int j = threadIdx.x; j < D; j += blockDim.x) {
@@ -351,7 +370,8 @@ __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const f
                     }
                 }
             }
-            out[head * D + j] = __float2bfloat16_rn(l_sum > 0.0f ? acc / l_sum : 0.0f);
+            out[head * D + j] = __float2bfloat16_rn(has_sink ? acc * inverse_sum_with_sink(m_star, l_sum, sink_log2)
+                                                             : (l_sum > 0.0f ? acc / l_sum : 0.0f));
         }
         return;
     }
@@ -366,7 +386,8 @@ __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const f
                 l_sum += weight * partial_ml[(head * splits + s) * 2 + 1];
             }
         }
-        out[head * D + j] = __float2bfloat16_rn(l_sum > 0.0f ? acc / l_sum : 0.0f);
+        out[head * D + j] = __float2bfloat16_rn(has_sink ? acc * inverse_sum_with_sink(m_star, l_sum, sink_log2)
+                                                         : (l_sum > 0.0f ? acc / l_sum : 0.0f));
     }
 }
 
@@ -380,7 +401,8 @@ __global__ void __launch_bounds__(kThreads, EXACT ? 2 : 3) prefill_attention_ker
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, int num_requests, int max_pages, int nq, int nkv,
-    int page_size, float scale_log2, int window, int token_offset, const float* __restrict__ slopes) {
+    int page_size, float scale_log2, int window, int token_offset, const float* __restrict__ slopes,
+    const float* __restrict__ sinks) {
     // token_offset: row of q and out at which the first of these requests begins (requests ahead of
     // them in the batch are another launch's); query_start holds rows of the whole batch.
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -554,7 +576,12 @@ __global__ void __launch_bounds__(kThreads, EXACT ? 2 : 3) prefill_attention_ker
 
     l_a = quad_sum(l_a);
     l_b = quad_sum(l_b);
-    const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
+    float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
+    if (EXACT && sinks != nullptr) {
+        const float sink_log2 = sinks[head] * kLog2e;
+        inv_a = inverse_sum_with_sink(m_a, l_a, sink_log2);
+        inv_b = inverse_sum_with_sink(m_b, l_b, sink_log2);
+    }
     bf16* out_tile = out + ((size_t)(q_begin + tile_first) * nq + head) * D;
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
@@ -570,7 +597,7 @@ template <int D, bool EXACT = false>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o,
                   float* partial_ml, const int* seq_lens, const int* block_table, int num_requests,
                   int max_pages, int nq, int nkv, int page_size, float scale, int window, int splits,
-                  cudaStream_t stream, const float* slopes = nullptr) {
+                  cudaStream_t stream, const float* slopes = nullptr, const float* sinks = nullptr) {
     auto kernel = decode_attention_kernel<D, EXACT>;
     const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -578,11 +605,12 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     dim3 grid(splits, nkv, num_requests);
     launch_overlapped(kernel, grid, kThreads, smem, stream,
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, partial_o, partial_ml,
-        seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits, slopes);
+        seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits, slopes, sinks);
     if (int rc = check_launch("decode_attention")) return rc;
     if (splits > 1) {
         launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,
-                          (const float*)partial_o, (const float*)partial_ml, (bf16*)out, splits);
+                          (const float*)partial_o, (const float*)partial_ml, (bf16*)out, splits,
+                          EXACT ? sinks : (const float*)nullptr, nq);
         return check_launch("merge_splits");
     }
     return 0;
@@ -592,7 +620,8 @@ template <int D, bool EXACT = false>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                    const int* query_start, const int* seq_lens, const int* block_table,
                    int num_requests, int num_tokens, int max_pages, int nq, int nkv, int page_size,
-                   float scale, int window, int token_offset, cudaStream_t stream, const float* slopes = nullptr) {
+                   float scale, int window, int token_offset, cudaStream_t stream, const float* slopes = nullptr,
+                   const float* sinks = nullptr) {
     auto kernel = prefill_attention_kernel<D, EXACT>;
     const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -600,7 +629,8 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void
     dim3 grid((num_tokens - token_offset) / 64 + num_requests, nq);
     kernel<<<grid, kThreads, smem, stream>>>(
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, query_start, seq_lens,
-        block_table, num_requests, max_pages, nq, nkv, page_size, scale * kLog2e, window, token_offset, slopes);
+        block_table, num_requests, max_pages, nq, nkv, page_size, scale * kLog2e, window, token_offset, slopes,
+        sinks);
     return check_launch("prefill_attention");
 }
 

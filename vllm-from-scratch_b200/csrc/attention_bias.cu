@@ -24,7 +24,7 @@ __global__ void head_norm_scale_cache_kernel(
     const T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
     const float* __restrict__ q_weight, const float* __restrict__ k_weight, T* __restrict__ q_out,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int d, int dv, int page_size, float eps,
-    float temp_coef, int temp_every) {
+    float temp_coef, int temp_every, int row_stride, int norm_q, int norm_k) {
     overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
     overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     const int token = blockIdx.x;
@@ -35,7 +35,7 @@ __global__ void head_norm_scale_cache_kernel(
     const bool is_q = head_slot < nq;
     const bool is_k = !is_q && head_slot < nq + nkv;
     if (!is_q && k_pages == nullptr) return;
-    const size_t row = (size_t)token * ((size_t)(nq + nkv) * d + (size_t)nkv * dv);
+    const size_t row = (size_t)token * (size_t)row_stride;
     int slot = 0;
     if (!is_q) {
         slot = slots[token];
@@ -43,6 +43,7 @@ __global__ void head_norm_scale_cache_kernel(
     }
     const int page = slot / page_size, offset = slot - page * page_size;
     if (!is_q && !is_k) {
+        if (dv == 0) return;                // keys only: they serve as the values too
         const int kv_head = head_slot - nq - nkv;
         const T* src = qkv + row + (size_t)(nq + nkv) * d + (size_t)kv_head * dv;
         T* dst = v_pages + (((size_t)page * nkv + kv_head) * page_size + offset) * dv;
@@ -52,7 +53,7 @@ __global__ void head_norm_scale_cache_kernel(
     const T* src = qkv + row + (size_t)head_slot * d;
     const float* weight = is_q ? q_weight : k_weight;
     float factor = 1.0f;
-    if (weight) {
+    if (is_q ? norm_q : norm_k) {           // with or without a weight vector
         float sum_sq = 0.0f;
         for (int j = lane; j < d; j += 32) {
             const float v = to_float(src[j]);
@@ -81,8 +82,8 @@ template <typename T, int DPL>  // DPL: value elements per lane, dv <= 32 * DPL
 __global__ void __launch_bounds__(kWarps * 32) biased_paged_attention_kernel(
     const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     T* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
-    const int* __restrict__ block_table, const float* __restrict__ slopes, int num_requests, int max_pages,
-    int nq, int nkv, int d, int dv, int page_size, float scale, int window) {
+    const int* __restrict__ block_table, const float* __restrict__ slopes, const float* __restrict__ sinks,
+    int num_requests, int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale, int window) {
     overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
     overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     extern __shared__ float smem[];
@@ -197,7 +198,13 @@ __global__ void __launch_bounds__(kWarps * 32) biased_paged_attention_kernel(
     for (int r = 0; r < kRowsPerWarp; ++r) {
         const int row = warp * kRowsPerWarp + r;
         if (row >= rows_here) continue;
-        const float inv = row_sum[r] > 0.0f ? 1.0f / row_sum[r] : 0.0f;
+        float inv = row_sum[r] > 0.0f ? 1.0f / row_sum[r] : 0.0f;
+        if (sinks != nullptr && row_max[r] != -INFINITY) {
+            // one more term exp(sink) in the denominator, with no key and no value
+            const float sink = sinks[head], top = fmaxf(row_max[r], sink);
+            const float keep = expf(row_max[r] - top);
+            inv = keep / (row_sum[r] * keep + expf(sink - top));
+        }
         T* dst = out + ((size_t)(q_begin + tile_first + row) * nq + head) * dv;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
@@ -209,9 +216,9 @@ __global__ void __launch_bounds__(kWarps * 32) biased_paged_attention_kernel(
 
 template <typename T, int DPL>
 int launch_biased(const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
-                  const int* seq_lens, const int* block_table, const float* slopes, int num_requests, int num_tokens,
-                  int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale, int window,
-                  cudaStream_t stream) {
+                  const int* seq_lens, const int* block_table, const float* slopes, const float* sinks,
+                  int num_requests, int num_tokens, int max_pages, int nq, int nkv, int d, int dv, int page_size,
+                  float scale, int window, cudaStream_t stream) {
     auto kernel = biased_paged_attention_kernel<T, DPL>;
     const size_t smem = sizeof(float) * ((size_t)kQueryTile * d + (size_t)kKeyTile * (d + 1) + (size_t)kKeyTile * dv);
     if (smem > 48 * 1024) {
@@ -220,21 +227,21 @@ int launch_biased(const void* q, const void* k_pages, const void* v_pages, void*
     }
     dim3 grid(num_tokens / kQueryTile + num_requests, nq);
     launch_overlapped_if(num_tokens <= kOverlapMostRows, kernel, grid, kWarps * 32, smem, stream,
-        (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, query_start, seq_lens, block_table, slopes,
+        (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, query_start, seq_lens, block_table, slopes, sinks,
         num_requests, max_pages, nq, nkv, d, dv, page_size, scale, window);
     return check_launch("biased_paged_attention");
 }
 
 template <typename T>
 int dispatch_biased(const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
-                    const int* seq_lens, const int* block_table, const float* slopes, int num_requests,
-                    int num_tokens, int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale,
-                    int window, cudaStream_t stream) {
+                    const int* seq_lens, const int* block_table, const float* slopes, const float* sinks,
+                    int num_requests, int num_tokens, int max_pages, int nq, int nkv, int d, int dv, int page_size,
+                    float scale, int window, cudaStream_t stream) {
 #define B200_CASE(DPL)                                                                                       \
     if (dv <= 32 * DPL)                                                                                      \
         return launch_biased<T, DPL>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes,   \
-                                     num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size, scale,  \
-                                     window, stream);
+                                     sinks, num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size,  \
+                                     scale, window, stream);
     B200_CASE(1) B200_CASE(2) B200_CASE(4) B200_CASE(8) B200_CASE(16)
 #undef B200_CASE
     return fail("biased_paged_attention", "value heads above 512 are not built");
@@ -242,17 +249,22 @@ int dispatch_biased(const void* q, const void* k_pages, const void* v_pages, voi
 
 }  // namespace b200
 
-// qkv rows: [nq * d | nkv * d | nkv * dv].  q_weight / k_weight may be null (no head norm),
-// temp_every <= 0 means no temperature, k_pages / v_pages may be null (nothing is stored).
+// qkv rows: [nq * d | nkv * d | nkv * dv], `row_stride` elements apart (0: packed).  norm_q / norm_k: whether
+// queries / keys are divided by their root mean square per head; q_weight / k_weight may be null (no weight
+// vector behind that norm).  temp_every <= 0 means no temperature, k_pages / v_pages may be null (nothing is
+// stored), dv = 0 stores keys only (nq = 0 with it: rows of keys alone, normalised into their pages).
 // dtype: 0 = float32, 1 = bfloat16.
 B200_EXPORT int b200_head_norm_scale_cache(
     const void* qkv, const int* positions, const int* slots, const float* q_weight, const float* k_weight,
     void* q_out, void* k_pages, void* v_pages, int num_tokens, int nq, int nkv, int d, int dv, int page_size,
-    float eps, float temp_coef, int temp_every, int dtype, cudaStream_t stream) {
+    float eps, float temp_coef, int temp_every, int row_stride, int norm_q, int norm_k, int dtype,
+    cudaStream_t stream) {
     using namespace b200;
     if (num_tokens == 0) return 0;
-    if ((k_pages == nullptr) != (v_pages == nullptr))
+    if (dv > 0 && (k_pages == nullptr) != (v_pages == nullptr))
         return fail("head_norm_scale_cache", "key and value pages must be given together");
+    if (row_stride <= 0) row_stride = (nq + nkv) * d + nkv * dv;
+    if (row_stride < (nq + nkv) * d + nkv * dv) return fail("head_norm_scale_cache", "row stride below the row's width");
     if (k_pages && page_size <= 0) return fail("head_norm_scale_cache", "page_size must be positive");
     const int warps = 4;
     dim3 grid(num_tokens, (nq + 2 * nkv + warps - 1) / warps);
@@ -260,33 +272,38 @@ B200_EXPORT int b200_head_norm_scale_cache(
     if (dtype == 0)
         launch_overlapped_if(num_tokens <= kOverlapMostRows, head_norm_scale_cache_kernel<float>, grid, warps * 32, 0, stream,
             (const float*)qkv, positions, slots, q_weight, k_weight, (float*)q_out, (float*)k_pages, (float*)v_pages,
-            nq, nkv, d, dv, page_size, eps, temp_coef, temp_every);
+            nq, nkv, d, dv, page_size, eps, temp_coef, temp_every, row_stride, norm_q, norm_k);
     else if (dtype == 1)
         launch_overlapped_if(num_tokens <= kOverlapMostRows, head_norm_scale_cache_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream,
             (const __nv_bfloat16*)qkv, positions, slots, q_weight, k_weight, (__nv_bfloat16*)q_out,
-            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, nq, nkv, d, dv, page_size, eps, temp_coef, temp_every);
+            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, nq, nkv, d, dv, page_size, eps, temp_coef, temp_every,
+            row_stride, norm_q, norm_k);
     else
         return fail("head_norm_scale_cache", "dtype must be 0 (float32) or 1 (bfloat16)");
     return check_launch("head_norm_scale_cache");
 }
 
-// slopes: float32 [nq] or null (no bias).  window <= 0: every earlier key is visible.
+// slopes: float32 [nq] or null (no bias).  sinks: float32 [nq] or null; a head's sink is one more term
+// exp(sink) in its softmax denominator, unscaled, without a key or a value.  window <= 0: every earlier
+// key is visible.
 B200_EXPORT int b200_biased_paged_attention(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start, const int* seq_lens,
-    const int* block_table, const float* slopes, int num_requests, int num_tokens, int max_pages, int nq, int nkv,
-    int d, int dv, int page_size, float scale, int window, int dtype, cudaStream_t stream) {
+    const int* block_table, const float* slopes, const float* sinks, int num_requests, int num_tokens,
+    int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale, int window, int dtype,
+    cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0 || num_tokens == 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv) return fail("biased_paged_attention", "query heads must be a multiple of key/value heads");
     if (nq > 65535) return fail("biased_paged_attention", "more than 65535 query heads");
     if (d <= 0 || dv <= 0 || page_size <= 0 || max_pages <= 0) return fail("biased_paged_attention", "sizes must be positive");
     if (dtype == 0)
-        return dispatch_biased<float>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes, num_requests,
-                                      num_tokens, max_pages, nq, nkv, d, dv, page_size, scale, window, stream);
+        return dispatch_biased<float>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes, sinks,
+                                      num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size, scale, window,
+                                      stream);
     if (dtype == 1)
         return dispatch_biased<__nv_bfloat16>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes,
-                                              num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size, scale,
-                                              window, stream);
+                                              sinks, num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size,
+                                              scale, window, stream);
     return fail("biased_paged_attention", "dtype must be 0 (float32) or 1 (bfloat16)");
 }
 
@@ -303,8 +320,8 @@ B200_EXPORT int b200_biased_sm_count() { return b200::sm_count(); }
 // [requests * nq * splits * d] floats and partial_ml [requests * nq * splits * 2] floats of scratch.
 B200_EXPORT int b200_biased_decode_attention_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o, float* partial_ml,
-    const int* seq_lens, const int* block_table, const float* slopes, int num_requests, int max_pages, int nq,
-    int nkv, int d, int page_size, float scale, int window, int splits, cudaStream_t stream) {
+    const int* seq_lens, const int* block_table, const float* slopes, const float* sinks, int num_requests,
+    int max_pages, int nq, int nkv, int d, int page_size, float scale, int window, int splits, cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0) return 0;
     if (!b200_biased_attention_bf16_supports(nq, nkv, d, d)) return fail("biased_decode_attention", "shape not built");
@@ -315,7 +332,7 @@ B200_EXPORT int b200_biased_decode_attention_bf16(
     if (d == D)                                                                                              \
         return launch_decode<D, true>(q, k_pages, v_pages, out, partial_o, partial_ml, seq_lens, block_table, \
                                       num_requests, max_pages, nq, nkv, page_size, scale, window, splits,    \
-                                      stream, slopes);
+                                      stream, slopes, sinks);
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("biased_decode_attention", "head_dim not built");
@@ -325,8 +342,8 @@ B200_EXPORT int b200_biased_decode_attention_bf16(
 // requests given here begin at row token_offset.
 B200_EXPORT int b200_biased_prefill_attention_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start, const int* seq_lens,
-    const int* block_table, const float* slopes, int num_requests, int num_tokens, int max_pages, int nq, int nkv,
-    int d, int page_size, float scale, int window, int token_offset, cudaStream_t stream) {
+    const int* block_table, const float* slopes, const float* sinks, int num_requests, int num_tokens, int max_pages,
+    int nq, int nkv, int d, int page_size, float scale, int window, int token_offset, cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0 || num_tokens - token_offset <= 0) return 0;
     if (token_offset < 0) return fail("biased_prefill_attention", "negative token offset");
@@ -335,7 +352,7 @@ B200_EXPORT int b200_biased_prefill_attention_bf16(
     if (d == D)                                                                                                \
         return launch_prefill<D, true>(q, k_pages, v_pages, out, query_start, seq_lens, block_table,           \
                                        num_requests, num_tokens, max_pages, nq, nkv, page_size, scale, window, \
-                                       token_offset, stream, slopes);
+                                       token_offset, stream, slopes, sinks);
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("biased_prefill_attention", "head_dim not built");

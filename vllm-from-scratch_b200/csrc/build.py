@@ -32,7 +32,7 @@ EXTRA_FLAGS: dict[str, list[str]] = {
     "gemm_bf16": ["-lcuda"],
 }
 LIBRARIES = ("norm", "rope_cache", "attention_generic", "gemm_f32", "attention_bf16", "gemm_bf16",
-             "sampling", "decode_attention_static", "norm_ext", "attention_bias", "recurrence")
+             "sampling", "decode_attention_static", "norm_ext", "attention_bias", "recurrence", "grouped")
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -379,7 +379,8 @@ int launch_decode_tma(const CUtensorMap& map_k, const CUtensorMap& map_v, const 
     if (int rc = check_launch("decode_attention")) return rc;
     if (splits > 1) {
         launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,
-                          (const float*)partial_o, (const float*)partial_ml, (bf16*)out, splits);
+                          (const float*)partial_o, (const float*)partial_ml, (bf16*)out, splits,
+                          (const float*)nullptr, 1);
         return check_launch("merge_splits");
     }
     return 0;

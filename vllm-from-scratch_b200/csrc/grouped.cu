@@ -1,0 +1,573 @@
+// Products in groups, and what a routed feed-forward needs around them.
+//
+//   route_experts      router logits in float32, sigmoid scores, a correction added for the choice
+//                      only, the best groups of neighbouring experts, the `top` best experts of
+//                      those groups; weights are the plain scores of the chosen
+//   expert_lists       from the chosen experts of every token: how many rows each expert has, where
+//                      its rows begin, and each (token, choice) pair's row
+//   grouped_gemm       C_g = A_g W_g^T for every group g, W_g [N, K] row-major.  The rows of a group
+//                      are either the same rows for every group at a column offset of its own (heads:
+//                      A and C hold the groups side by side in every row) or a list per group (experts:
+//                      rows gathered from the tokens, written one after another).  bfloat16: mma.sync
+//                      m16n8k16 with float32 accumulation; float32: fused multiply-adds in the order
+//                      of k.  GATED: W_g holds 2 N rows, gate rows first, and C = act(gate) * up.
+//   combine_experts    y_t = sum over a token's choices of weight * its row, in float32, in the
+//                      order of the choices
+//   capped_swish_mul   out = g * sigmoid(slope g) * (u + offset), g = min(gate, limit), u = clamp(up)
+//   gelu_gate_rows     out = gelu_tanh(g) * table[id, column ...]
+//
+// A row's result never depends on which other rows share its tile: every output element is one
+// chain of products over k in a fixed order.
+#include "common.cuh"
+
+namespace b200 {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ float sigmoid_fn(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ------------------------------------------------------------------------------- routing
+// (value, index) pairs in the order "larger value first, then smaller index": true if a comes before b.
+__device__ __forceinline__ bool ahead(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+
+template <typename T>
+__global__ void route_experts_kernel(const T* __restrict__ x, const float* __restrict__ router,
+                                     const float* __restrict__ correction, int* __restrict__ ids,
+                                     float* __restrict__ weights, int K, int E, int top, int group_count,
+                                     int group_keep, int group_top) {
+    overlap_trigger();
+    overlap_wait();
+    extern __shared__ float route_smem[];
+    float* score = route_smem;              // [E] sigmoid of the logit
+    float* choice = score + E;              // [E] score + correction, -inf outside the kept groups
+    float* marks = choice + E;              // [group_count]
+    const int token = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const T* row = x + (size_t)token * K;
+    for (int e = warp; e < E; e += warps) {
+        const float* w = router + (size_t)e * K;
+        float sum = 0.0f;
+        for (int k = lane; k < K; k += 32) sum = fmaf(w[k], to_float(row[k]), sum);
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            const float s = sigmoid_fn(sum);
+            score[e] = s;
+            choice[e] = correction ? s + correction[e] : s;
+        }
+    }
+    __syncthreads();
+    if (group_count > 1 && group_keep < group_count) {
+        const int per = E / group_count;
+        for (int g = threadIdx.x; g < group_count; g += blockDim.x) {
+            // the sum of the group's `group_top` largest choice scores
+            float sum = 0.0f, pv = INFINITY;
+            int pi = -1;
+            for (int j = 0; j < group_top && j < per; ++j) {
+                float bv = -INFINITY;
+                int bi = -1;
+                for (int i = 0; i < per; ++i) {
+                    const float v = choice[g * per + i];
+                    if (!(pi < 0 || ahead(pv, pi, v, i))) continue;       // taken already
+                    if (bi < 0 || ahead(v, i, bv, bi)) { bv = v; bi = i; }
+                }
+                sum += bv;
+                pv = bv;
+                pi = bi;
+            }
+            marks[g] = sum;
+        }
+        __syncthreads();
+        // A group is kept if fewer than `group_keep` groups come before it.
+        for (int g = threadIdx.x; g < group_count; g += blockDim.x) {
+            int before = 0;
+            for (int o = 0; o < group_count; ++o)
+                if (o != g && ahead(marks[o], o, marks[g], g)) ++before;
+            if (before >= group_keep)
+                for (int i = 0; i < per; ++i) choice[g * per + i] = -INFINITY;
+        }
+        __syncthreads();
+    }
+    if (warp != 0) return;
+    float pv = INFINITY;
+    int pi = -1;
+    for (int j = 0; j < top; ++j) {
+        float bv = -INFINITY;
+        int bi = -1;
+        for (int e = lane; e < E; e += 32) {
+            const float v = choice[e];
+            if (!(pi < 0 || ahead(pv, pi, v, e))) continue;
+            if (bi < 0 || ahead(v, e, bv, bi)) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+            if (oi >= 0 && (bi < 0 || ahead(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+        }
+        if (bi < 0) bi = 0;         // fewer candidates than choices: cannot happen with top <= E
+        if (lane == 0) {
+            ids[(size_t)token * top + j] = bi;
+            weights[(size_t)token * top + j] = score[bi];
+        }
+        pv = bv;
+        pi = bi;
+    }
+}
+
+// One block.  offsets [E + 1]; sorted_pair [pairs]: the pairs (token * top + choice) expert by expert;
+// position [pairs]: the row of each pair.
+__global__ void expert_lists_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__ offsets,
+                                    int* __restrict__ sorted_pair, int* __restrict__ position) {
+    overlap_trigger();
+    overlap_wait();
+    extern __shared__ int list_smem[];
+    int* counts = list_smem;                // [E], then the running cursor of each expert
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int running = 0;
+        for (int e = 0; e < E; ++e) {
+            const int count = counts[e];
+            offsets[e] = running;
+            counts[e] = running;
+            running += count;
+        }
+        offsets[E] = running;
+    }
+    __syncthreads();
+    // Pairs of one expert keep no particular order among themselves; a row's result does not depend
+    // on where in its expert's list it stands.
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e < 0 || e >= E) { position[p] = -1; continue; }
+        const int row = atomicAdd(&counts[e], 1);
+        sorted_pair[row] = p;
+        position[p] = row;
+    }
+}
+
+template <typename T>
+__global__ void combine_experts_kernel(const T* __restrict__ rows, const int* __restrict__ position,
+                                       const float* __restrict__ weights, T* __restrict__ out, int width, int top) {
+    overlap_trigger();
+    overlap_wait();
+    const int token = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float sum = 0.0f;
+        for (int j = 0; j < top; ++j) {
+            const int row = position[(size_t)token * top + j];
+            if (row >= 0) sum = fmaf(weights[(size_t)token * top + j], to_float(rows[(size_t)row * width + i]), sum);
+        }
+        out[(size_t)token * width + i] = from_float<T>(sum);
+    }
+}
+
+// ----------------------------------------------------------------------- grouped products
+struct GroupedArgs {
+    const void* a;          // rows of A
+    const void* w;          // [groups][N (2 N when gated)][K]
+    void* c;
+    const int* offsets;     // [groups + 1] first row of each group's list, or null: every group has `rows` rows
+    const int* row_index;   // [rows of all lists] -> index, divided by `index_divisor` = row of A; null: the list's row
+    int index_divisor;
+    int rows;               // rows of a group without lists
+    int groups;
+    int N, K;
+    long long lda, ldc;     // elements between rows of A and of C
+    long long a_group, c_group;     // elements between groups within a row
+    float act_limit, act_slope, act_offset;     // gated epilogue, see gated_value
+    int act_kind;           // 0: silu(gate) * up; 1: capped: g sigmoid(slope g) (u + offset)
+};
+
+__device__ __forceinline__ float gated_value(float gate, float up, const GroupedArgs& p) {
+    if (p.act_kind == 0) return gate * sigmoid_fn(gate) * up;
+    const float g = fminf(gate, p.act_limit);
+    const float u = fminf(fmaxf(up, -p.act_limit), p.act_limit);
+    return g * sigmoid_fn(p.act_slope * g) * (u + p.act_offset);
+}
+
+constexpr int kBM = 32, kBN = 64, kThreadsG = 128;
+
+// Which group and which tile of its rows a block has: group g owns blocks [first(g), first(g + 1)) with
+// first(g) = offsets[g] / kBM + g, which leaves every group ceil(rows / kBM) blocks at least.
+__device__ __forceinline__ bool find_tile(const GroupedArgs& p, int block, int& group, int& row0, int& rows_here,
+                                          int& list_base) {
+    if (p.offsets == nullptr) {
+        const int tiles = (p.rows + kBM - 1) / kBM;
+        group = block / tiles;
+        row0 = (block - group * tiles) * kBM;
+        list_base = 0;
+        rows_here = min(kBM, p.rows - row0);
+        return group < p.groups && rows_here > 0;
+    }
+    int lo = 0, hi = p.groups - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (p.offsets[mid] / kBM + mid <= block) lo = mid; else hi = mid - 1;
+    }
+    group = lo;
+    list_base = p.offsets[group];
+    const int count = p.offsets[group + 1] - list_base;
+    row0 = (block - (list_base / kBM + group)) * kBM;
+    rows_here = min(kBM, count - row0);
+    return rows_here > 0;
+}
+
+__device__ __forceinline__ long long a_row_of(const GroupedArgs& p, int list_row) {
+    return p.row_index ? (long long)(p.row_index[list_row] / p.index_divisor) : (long long)list_row;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Eight consecutive bfloat16 of a row of K elements beginning at k; zeros past the end.
+__device__ __forceinline__ uint4 load8(const bf16* row, int k, int K, bool vector_ok) {
+    if (row == nullptr || k >= K) return make_uint4(0, 0, 0, 0);
+    if (vector_ok && k + 8 <= K) return *reinterpret_cast<const uint4*>(row + k);
+    union { uint4 v; bf16 e[8]; } u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) u.e[i] = k + i < K ? row[k + i] : __float2bfloat16_rn(0.0f);
+    return u.v;
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(kThreadsG) grouped_gemm_bf16_kernel(const GroupedArgs p) {
+    overlap_trigger();
+    overlap_wait();
+    constexpr int BK = 32, LD = BK + 8;
+    constexpr int NB = GATED ? 2 : 1;
+    __shared__ __align__(16) bf16 a_s[kBM][LD];
+    __shared__ __align__(16) bf16 b_s[NB][kBN][LD];
+    int group, row0, rows_here, list_base;
+    if (!find_tile(p, blockIdx.x, group, row0, rows_here, list_base)) return;
+    const int n0 = blockIdx.y * kBN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp >> 1, wn = warp & 1;
+    const int K = p.K, N = p.N;
+    const bf16* a = (const bf16*)p.a + (long long)group * p.a_group;
+    const bf16* w = (const bf16*)p.w + (long long)group * (long long)(NB * N) * K;
+    const bool vector_ok = (K % 8 == 0) && (p.lda % 8 == 0) && (p.a_group % 8 == 0)
+                           && (((uintptr_t)p.a | (uintptr_t)p.w) & 15) == 0;
+
+    // This thread's share of a tile: one piece of eight of A, two of each B.
+    const int a_r = tid >> 2, a_k = (tid & 3) * 8;
+    const bf16* a_src = a_r < rows_here ? a + a_row_of(p, list_base + row0 + a_r) * p.lda : nullptr;
+    const bf16* b_src[NB][2];
+#pragma unroll
+    for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int n = n0 + (tid >> 2) + 32 * i;
+            b_src[h][i] = n < N ? w + ((long long)h * N + n) * K : nullptr;
+        }
+    float acc[NB][4][4];
+#pragma unroll
+    for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) acc[h][t][0] = acc[h][t][1] = acc[h][t][2] = acc[h][t][3] = 0.0f;
+
+    uint4 a_next = load8(a_src, a_k, K, vector_ok);
+    uint4 b_next[NB][2];
+#pragma unroll
+    for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) b_next[h][i] = load8(b_src[h][i], a_k, K, vector_ok);
+
+    const int g = lane >> 2, t4 = lane & 3;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        __syncthreads();
+        *reinterpret_cast<uint4*>(&a_s[a_r][a_k]) = a_next;
+#pragma unroll
+        for (int h = 0; h < NB; ++h)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) *reinterpret_cast<uint4*>(&b_s[h][(tid >> 2) + 32 * i][a_k]) = b_next[h][i];
+        __syncthreads();
+        if (k0 + BK < K) {
+            a_next = load8(a_src, k0 + BK + a_k, K, vector_ok);
+#pragma unroll
+            for (int h = 0; h < NB; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) b_next[h][i] = load8(b_src[h][i], k0 + BK + a_k, K, vector_ok);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BK; kk += 16) {
+            unsigned af[4];
+            af[0] = *reinterpret_cast<const unsigned*>(&a_s[wm * 16 + g][kk + 2 * t4]);
+            af[1] = *reinterpret_cast<const unsigned*>(&a_s[wm * 16 + g + 8][kk + 2 * t4]);
+            af[2] = *reinterpret_cast<const unsigned*>(&a_s[wm * 16 + g][kk + 2 * t4 + 8]);
+            af[3] = *reinterpret_cast<const unsigned*>(&a_s[wm * 16 + g + 8][kk + 2 * t4 + 8]);
+#pragma unroll
+            for (int h = 0; h < NB; ++h)
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int n = wn * 32 + t * 8 + g;
+                    const unsigned b0 = *reinterpret_cast<const unsigned*>(&b_s[h][n][kk + 2 * t4]);
+                    const unsigned b1 = *reinterpret_cast<const unsigned*>(&b_s[h][n][kk + 2 * t4 + 8]);
+                    mma_bf16(acc[h][t], af, b0, b1);
+                }
+        }
+    }
+
+    bf16* c = (bf16*)p.c + (long long)group * p.c_group;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = wm * 16 + g + 8 * half;
+        if (r >= rows_here) continue;
+        bf16* dst = c + (long long)(list_base + row0 + r) * p.ldc;
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int n = n0 + wn * 32 + t * 8 + 2 * t4 + e;
+                if (n >= N) continue;
+                float v = acc[0][t][2 * half + e];
+                if (GATED) {
+                    // both products are rounded as a projection's output is, then the activation in float32
+                    const float gate = __bfloat162float(__float2bfloat16_rn(v));
+                    const float up = __bfloat162float(__float2bfloat16_rn(acc[NB - 1][t][2 * half + e]));
+                    v = gated_value(gate, up, p);
+                }
+                dst[n] = __float2bfloat16_rn(v);
+            }
+    }
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(kThreadsG) grouped_gemm_f32_kernel(const GroupedArgs p) {
+    overlap_trigger();
+    overlap_wait();
+    constexpr int BK = 16;
+    constexpr int NB = GATED ? 2 : 1;
+    __shared__ float a_s[kBM][BK + 1];
+    __shared__ float b_s[NB][kBN][BK + 1];
+    int group, row0, rows_here, list_base;
+    if (!find_tile(p, blockIdx.x, group, row0, rows_here, list_base)) return;
+    const int n0 = blockIdx.y * kBN;
+    const int tid = threadIdx.x;
+    const int ty = tid >> 4, tx = tid & 15;         // rows ty * 4 + i, columns tx + 16 * j
+    const int K = p.K, N = p.N;
+    const float* a = (const float*)p.a + (long long)group * p.a_group;
+    const float* w = (const float*)p.w + (long long)group * (long long)(NB * N) * K;
+    float acc[NB][4][4];
+#pragma unroll
+    for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[h][i][0] = acc[h][i][1] = acc[h][i][2] = acc[h][i][3] = 0.0f;
+
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        __syncthreads();
+        for (int idx = tid; idx < kBM * BK; idx += kThreadsG) {
+            const int r = idx / BK, k = idx - r * BK;
+            float v = 0.0f;
+            if (r < rows_here && k0 + k < K) v = a[a_row_of(p, list_base + row0 + r) * p.lda + k0 + k];
+            a_s[r][k] = v;
+        }
+#pragma unroll
+        for (int h = 0; h < NB; ++h)
+            for (int idx = tid; idx < kBN * BK; idx += kThreadsG) {
+                const int n = idx / BK, k = idx - n * BK;
+                float v = 0.0f;
+                if (n0 + n < N && k0 + k < K) v = w[((long long)h * N + n0 + n) * K + k0 + k];
+                b_s[h][n][k] = v;
+            }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float av[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = a_s[ty * 4 + i][k];
+#pragma unroll
+            for (int h = 0; h < NB; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float bv = b_s[h][tx + 16 * j][k];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[h][i][j] = fmaf(av[i], bv, acc[h][i][j]);
+                }
+        }
+    }
+    float* c = (float*)p.c + (long long)group * p.c_group;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows_here) continue;
+        float* dst = c + (long long)(list_base + row0 + r) * p.ldc;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx + 16 * j;
+            if (n >= N) continue;
+            dst[n] = GATED ? gated_value(acc[0][i][j], acc[NB - 1][i][j], p) : acc[0][i][j];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------ elementwise
+template <typename T>
+__global__ void capped_swish_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, float limit,
+                                        float slope, float offset) {
+    overlap_trigger();
+    overlap_wait();
+    const size_t token = blockIdx.x;
+    const T* row = gate_up + token * 2 * (size_t)inter;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
+        const float g = fminf(to_float(row[i]), limit);
+        const float u = fminf(fmaxf(to_float(row[inter + i]), -limit), limit);
+        out[token * inter + i] = from_float<T>(g * sigmoid_fn(slope * g) * (u + offset));
+    }
+}
+
+__device__ __forceinline__ float gelu_tanh_fn(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void gelu_gate_rows_kernel(const T* __restrict__ gate, const T* __restrict__ table,
+                                      const int* __restrict__ ids, T* __restrict__ out, int dim, int table_stride,
+                                      int column, int vocab) {
+    overlap_trigger();
+    overlap_wait();
+    const size_t token = blockIdx.x;
+    const int id = ids[token];
+    const bool known = id >= 0 && id < vocab;       // the embedding reports an id outside the table
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float e = known ? to_float(table[(size_t)id * table_stride + column + i]) : 0.0f;
+        out[token * dim + i] = from_float<T>(gelu_tanh_fn(to_float(gate[token * dim + i])) * e);
+    }
+}
+
+}  // namespace b200
+
+// x [tokens, K] (dtype 0 float32, 1 bfloat16), router float32 [E, K], correction float32 [E] or null.
+// ids int32 [tokens, top], weights float32 [tokens, top].  Groups: `group_count` equal groups of
+// neighbouring experts, of which the `group_keep` with the largest sums of their `group_top` largest
+// choice scores stay eligible (group_count <= 1 or group_keep >= group_count: all do).
+B200_EXPORT int b200_route_experts(const void* x, const float* router, const float* correction, int* ids,
+                                   float* weights, int tokens, int K, int E, int top, int group_count,
+                                   int group_keep, int group_top, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (tokens == 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || K <= 0) return fail("route_experts", "sizes out of range");
+    if (group_count < 1) group_count = 1;
+    if (E % group_count) return fail("route_experts", "experts do not divide into equal groups");
+    if (group_keep < 1 || group_top < 1) return fail("route_experts", "group_keep and group_top must be positive");
+    if (top > (long long)min(group_keep, group_count) * (E / group_count))
+        return fail("route_experts", "the kept groups hold fewer experts than are to be chosen");
+    const size_t smem = sizeof(float) * (2 * (size_t)E + group_count);
+    if (smem > 48 * 1024) return fail("route_experts", "too many experts for one block's shared memory");
+    if (dtype == 0)
+        launch_overlapped_if(tokens <= kOverlapMostRows, route_experts_kernel<float>, tokens, 128, smem, stream,
+            (const float*)x, router, correction, ids, weights, K, E, top, group_count, group_keep, group_top);
+    else if (dtype == 1)
+        launch_overlapped_if(tokens <= kOverlapMostRows, route_experts_kernel<__nv_bfloat16>, tokens, 128, smem, stream,
+            (const __nv_bfloat16*)x, router, correction, ids, weights, K, E, top, group_count, group_keep, group_top);
+    else
+        return fail("route_experts", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("route_experts");
+}
+
+B200_EXPORT int b200_expert_lists(const int* ids, int pairs, int E, int* offsets, int* sorted_pair, int* position,
+                                  cudaStream_t stream) {
+    using namespace b200;
+    if (E <= 0 || pairs < 0) return fail("expert_lists", "sizes out of range");
+    if ((size_t)E * sizeof(int) > 48 * 1024) return fail("expert_lists", "too many experts for one block's shared memory");
+    launch_overlapped_if(pairs <= 8 * kOverlapMostRows, expert_lists_kernel, 1, pairs > 256 ? 1024 : 256,
+                         (size_t)E * sizeof(int), stream, ids, pairs, E, offsets, sorted_pair, position);
+    return check_launch("expert_lists");
+}
+
+B200_EXPORT int b200_combine_experts(const void* rows, const int* position, const float* weights, void* out,
+                                     int tokens, int width, int top, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (tokens == 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == 0)
+        launch_overlapped_if(tokens <= kOverlapMostRows, combine_experts_kernel<float>, tokens, threads, 0, stream,
+            (const float*)rows, position, weights, (float*)out, width, top);
+    else if (dtype == 1)
+        launch_overlapped_if(tokens <= kOverlapMostRows, combine_experts_kernel<__nv_bfloat16>, tokens, threads, 0, stream,
+            (const __nv_bfloat16*)rows, position, weights, (__nv_bfloat16*)out, width, top);
+    else
+        return fail("combine_experts", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("combine_experts");
+}
+
+// See GroupedArgs.  `list_rows`: with offsets, the number of rows over all lists (it bounds the grid).
+// gated: 0 plain; 1 silu(gate) * up; 2 the capped form with (limit, slope, offset).
+B200_EXPORT int b200_grouped_gemm(const void* a, const void* w, void* c, const int* offsets, const int* row_index,
+                                  int index_divisor, int rows, int list_rows, int groups, int N, int K,
+                                  long long lda, long long ldc, long long a_group, long long c_group, int gated,
+                                  float limit, float slope, float offset, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (groups <= 0 || N <= 0 || K <= 0) return fail("grouped_gemm", "sizes out of range");
+    if (row_index != nullptr && (offsets == nullptr || index_divisor <= 0))
+        return fail("grouped_gemm", "a row index goes with lists and a positive divisor");
+    long long tiles;
+    if (offsets == nullptr) {
+        if (rows <= 0) return 0;
+        tiles = (long long)groups * ((rows + kBM - 1) / kBM);
+    } else {
+        if (list_rows <= 0) return 0;
+        tiles = list_rows / kBM + groups;
+    }
+    const int n_tiles = (N + kBN - 1) / kBN;
+    if (tiles > 2147483647LL || n_tiles > 65535) return fail("grouped_gemm", "grid out of range");
+    GroupedArgs p;
+    p.a = a; p.w = w; p.c = c; p.offsets = offsets; p.row_index = row_index; p.index_divisor = index_divisor;
+    p.rows = rows; p.groups = groups; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.a_group = a_group;
+    p.c_group = c_group; p.act_limit = limit; p.act_slope = slope; p.act_offset = offset;
+    p.act_kind = gated == 2 ? 1 : 0;
+    const dim3 grid((unsigned)tiles, n_tiles);
+    const bool overlap = (offsets ? list_rows : rows) <= kOverlapMostRows;
+    if (dtype == 0) {
+        if (gated) launch_overlapped_if(overlap, grouped_gemm_f32_kernel<true>, grid, kThreadsG, 0, stream, p);
+        else launch_overlapped_if(overlap, grouped_gemm_f32_kernel<false>, grid, kThreadsG, 0, stream, p);
+    } else if (dtype == 1) {
+        if (gated) launch_overlapped_if(overlap, grouped_gemm_bf16_kernel<true>, grid, kThreadsG, 0, stream, p);
+        else launch_overlapped_if(overlap, grouped_gemm_bf16_kernel<false>, grid, kThreadsG, 0, stream, p);
+    } else {
+        return fail("grouped_gemm", "dtype must be 0 (float32) or 1 (bfloat16)");
+    }
+    return check_launch("grouped_gemm");
+}
+
+B200_EXPORT int b200_capped_swish_mul(const void* gate_up, void* out, int tokens, int inter, float limit,
+                                      float slope, float offset, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (tokens == 0 || inter == 0) return 0;
+    const dim3 grid(tokens, min(8, (inter + 1023) / 1024));
+    if (dtype == 0)
+        launch_overlapped_if(tokens <= kOverlapMostRows, capped_swish_mul_kernel<float>, grid, 256, 0, stream,
+            (const float*)gate_up, (float*)out, inter, limit, slope, offset);
+    else if (dtype == 1)
+        launch_overlapped_if(tokens <= kOverlapMostRows, capped_swish_mul_kernel<__nv_bfloat16>, grid, 256, 0, stream,
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, limit, slope, offset);
+    else
+        return fail("capped_swish_mul", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("capped_swish_mul");
+}
+
+B200_EXPORT int b200_gelu_gate_rows(const void* gate, const void* table, const int* ids, void* out, int tokens,
+                                    int dim, int table_stride, int column, int vocab, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (tokens == 0 || dim == 0) return 0;
+    if (column < 0 || column + dim > table_stride) return fail("gelu_gate_rows", "columns outside the table");
+    const int threads = dim >= 256 ? 256 : (dim + 31) / 32 * 32;
+    if (dtype == 0)
+        launch_overlapped_if(tokens <= kOverlapMostRows, gelu_gate_rows_kernel<float>, tokens, threads, 0, stream,
+            (const float*)gate, (const float*)table, ids, (float*)out, dim, table_stride, column, vocab);
+    else if (dtype == 1)
+        launch_overlapped_if(tokens <= kOverlapMostRows, gelu_gate_rows_kernel<__nv_bfloat16>, tokens, threads, 0, stream,
+            (const __nv_bfloat16*)gate, (const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, dim, table_stride,
+            column, vocab);
+    else
+        return fail("gelu_gate_rows", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("gelu_gate_rows");
+}

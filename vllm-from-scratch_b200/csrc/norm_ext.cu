@@ -2,7 +2,9 @@
 //
 //   add_normed_rmsnorm   residual += rms(x) * x_weight;  out = rms(residual) * weight
 //                        (a norm behind a sublayer, the sum, and the norm in front of the next
-//                        sublayer as one kernel; either half may be left out)
+//                        sublayer as one kernel; either half may be left out, and without
+//                        `weight` the output is the sum itself in the output's type: what a
+//                        sublayer reads where no norm stands in front of it)
 //   paired_norm_mean     out = (rms(a) * wa + rms(b) * wb) / 2      (two mixers side by side)
 //   gated_group_norm     out = rms_g(y * silu(z)) * w               (gate first, groups of channels)
 //                        out = rms_g(y) * w * sigmoid(z)            (gate behind the norm)
@@ -26,24 +28,27 @@ __global__ void add_normed_rmsnorm_kernel(const T* __restrict__ x, const float* 
     const size_t base = (size_t)row * hidden;
     const bool store = rows == nullptr;
     float sum_x = 0.0f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float v = to_float(x[base + i]);
-        sum_x = fmaf(v, v, sum_x);
-    }
-    const float inv_x = rsqrtf(block_sum(sum_x, scratch) / (float)hidden + x_eps);
+    if (x != nullptr)
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = to_float(x[base + i]);
+            sum_x = fmaf(v, v, sum_x);
+        }
+    const float inv_x = x != nullptr ? rsqrtf(block_sum(sum_x, scratch) / (float)hidden + x_eps) : 0.0f;
     float sum_sq = 0.0f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float v = residual[base + i] + to_float(x[base + i]) * inv_x * x_weight[i];
-        if (store) residual[base + i] = v;
+        const float v = x != nullptr ? residual[base + i] + to_float(x[base + i]) * inv_x * x_weight[i] : residual[base + i];
+        if (store && x != nullptr) residual[base + i] = v;
         sum_sq = fmaf(v, v, sum_sq);
     }
     if (out == nullptr) return;
-    const float inv = rsqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
+    // weight == nullptr: the rows of the sum themselves, rounded to the output's type.
+    const float inv = weight != nullptr ? rsqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps) : 1.0f;
     const size_t out_base = (size_t)out_row * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         // The thread that stored an element reads it back; gathered rows form the sum again.
-        const float v = store ? residual[base + i] : residual[base + i] + to_float(x[base + i]) * inv_x * x_weight[i];
-        out[out_base + i] = from_float<T>(v * inv * weight[i]);
+        const float v = (store || x == nullptr) ? residual[base + i]
+                                                : residual[base + i] + to_float(x[base + i]) * inv_x * x_weight[i];
+        out[out_base + i] = from_float<T>(weight != nullptr ? v * inv * weight[i] : v);
     }
 }
 
@@ -107,35 +112,40 @@ __global__ void add_normed_rmsnorm_vec_kernel(const T* __restrict__ x, const flo
     for (int step = 0; step < kRowSteps; ++step) {
         const int i = (step * blockDim.x + threadIdx.x) * 4;
         if (i < hidden) {
-            xv[step] = load4(x + base + i);
+            xv[step] = x != nullptr ? load4(x + base + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             rv[step] = load4(residual + base + i);
             sum_x += dot4(xv[step]);
         }
     }
-    const float inv_x = rsqrtf(block_sum(sum_x, scratch) / (float)hidden + x_eps);
+    const float inv_x = x != nullptr ? rsqrtf(block_sum(sum_x, scratch) / (float)hidden + x_eps) : 0.0f;
     float sum_sq = 0.0f;
 #pragma unroll
     for (int step = 0; step < kRowSteps; ++step) {
         const int i = (step * blockDim.x + threadIdx.x) * 4;
         if (i < hidden) {
-            const float4 w = load4(x_weight + i);
             float4 v = rv[step];
-            v.x += xv[step].x * inv_x * w.x; v.y += xv[step].y * inv_x * w.y;
-            v.z += xv[step].z * inv_x * w.z; v.w += xv[step].w * inv_x * w.w;
-            if (rows == nullptr) store4(residual + base + i, v);
+            if (x != nullptr) {
+                const float4 w = load4(x_weight + i);
+                v.x += xv[step].x * inv_x * w.x; v.y += xv[step].y * inv_x * w.y;
+                v.z += xv[step].z * inv_x * w.z; v.w += xv[step].w * inv_x * w.w;
+                if (rows == nullptr) store4(residual + base + i, v);
+            }
             sum_sq += dot4(v);
             rv[step] = v;
         }
     }
     if (out == nullptr) return;
-    const float inv = rsqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
+    // weight == nullptr: the rows of the sum themselves, rounded to the output's type.
+    const float inv = weight != nullptr ? rsqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps) : 1.0f;
     const size_t out_base = (size_t)out_row * hidden;
 #pragma unroll
     for (int step = 0; step < kRowSteps; ++step) {
         const int i = (step * blockDim.x + threadIdx.x) * 4;
         if (i < hidden) {
-            const float4 w = load4(weight + i), v = rv[step];
-            store4(out + out_base + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+            const float4 v = rv[step];
+            const float4 w = weight != nullptr ? load4(weight + i) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            store4(out + out_base + i, weight != nullptr
+                ? make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w) : v);
         }
     }
 }
@@ -336,7 +346,9 @@ B200_EXPORT int b200_add_normed_rmsnorm(const void* x, const float* x_weight, fl
     using namespace b200;
     if (num_rows == 0) return 0;
     if (num_rows < 0 || hidden <= 0) return fail("add_normed_rmsnorm", "negative row count or width");
-    if ((weight == nullptr) != (out == nullptr)) return fail("add_normed_rmsnorm", "weight and out go together");
+    if (weight != nullptr && out == nullptr) return fail("add_normed_rmsnorm", "a norm weight without an output");
+    if (x == nullptr && out == nullptr) return 0;
+    if (x != nullptr && x_weight == nullptr) return fail("add_normed_rmsnorm", "an addend without its norm weight");
     const uintptr_t addresses = (uintptr_t)x | (uintptr_t)x_weight | (uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out;
     if (hidden % 4 == 0 && (addresses & 15) == 0 && vec_threads(hidden) > 0 && (dtype == 0 || dtype == 1)) {
         const int threads = vec_threads(hidden);

@@ -1,0 +1,128 @@
+"""Python face of the kernels for products in groups (a matrix per expert, a matrix per head), for
+routing tokens to experts, and for the gated activations that go with them (``csrc/grouped.cu``).
+
+As everywhere in this package there is no CPU or library alternative behind these functions.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _F, _I, _P, KernelError, _check, _code, _run, _stream
+
+_RUN = (torch.float32, torch.bfloat16)
+_L = ctypes.c_longlong
+
+GATE_NONE, GATE_SILU, GATE_CAPPED = 0, 1, 2
+
+
+def route_experts(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, ids: torch.Tensor,
+                  weights: torch.Tensor, top: int, group_count: int = 1, group_keep: int = 1,
+                  group_top: int = 2) -> None:
+    """For every row of ``x`` ``[T, K]``: logits ``router @ x`` in float32 (``router`` float32 ``[E, K]``),
+    scores = sigmoid; the ``top`` experts with the largest ``score + correction`` among the experts of
+    the ``group_keep`` best of ``group_count`` equal groups of neighbours (a group's mark: the sum of its
+    ``group_top`` largest ``score + correction``) go to ``ids`` (int32 ``[T, top]``), their plain scores
+    to ``weights`` (float32 ``[T, top]``).  Ties go to the smaller index."""
+    tokens, k = x.shape
+    experts = router.shape[0]
+    _run("grouped", "b200_route_experts",
+         _P(_check("router input", x, _RUN)), _P(_check("router matrix", router, torch.float32, (experts, k))),
+         _P(_check("score correction", correction, torch.float32, (experts,), optional=True)),
+         _P(_check("chosen experts", ids, torch.int32, (tokens, top))),
+         _P(_check("weights of the chosen", weights, torch.float32, (tokens, top))),
+         _I(tokens), _I(k), _I(experts), _I(top), _I(group_count), _I(group_keep), _I(group_top),
+         _I(_code(x.dtype)), _stream())
+
+
+def expert_lists(ids: torch.Tensor, experts: int, offsets: torch.Tensor, sorted_pair: torch.Tensor,
+                 position: torch.Tensor) -> None:
+    """From ``ids`` (int32 ``[T, top]``): ``offsets`` (int32 ``[experts + 1]``) where each expert's rows
+    begin, ``sorted_pair`` (int32 ``[T * top]``) the pairs ``token * top + choice`` expert by expert, and
+    ``position`` (int32 ``[T * top]``) the row of each pair."""
+    pairs = ids.numel()
+    _run("grouped", "b200_expert_lists", _P(_check("chosen experts", ids, torch.int32)), _I(pairs), _I(experts),
+         _P(_check("list offsets", offsets, torch.int32, (experts + 1,))),
+         _P(_check("sorted pairs", sorted_pair, torch.int32, (pairs,))),
+         _P(_check("rows of the pairs", position, torch.int32, (pairs,))), _stream())
+
+
+def combine_experts(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t] = sum_j weights[t, j] * rows[position[t * top + j]]`` in float32, j in order."""
+    tokens, width = out.shape
+    top = weights.shape[1]
+    _run("grouped", "b200_combine_experts", _P(_check("expert rows", rows, out.dtype, (None, width))),
+         _P(_check("rows of the pairs", position, torch.int32, (tokens * top,))),
+         _P(_check("weights", weights, torch.float32, (tokens, top))), _P(_check("combined output", out, _RUN)),
+         _I(tokens), _I(width), _I(top), _I(_code(out.dtype)), _stream())
+
+
+def _gate(gated) -> tuple[int, float, float, float]:
+    if gated is None:
+        return GATE_NONE, 0.0, 0.0, 0.0
+    if gated == "silu":
+        return GATE_SILU, 0.0, 0.0, 0.0
+    kind, limit, slope, offset = gated
+    if kind != "capped":
+        raise KernelError(f"gated epilogue {gated!r}: 'silu' or ('capped', limit, slope, offset)")
+    return GATE_CAPPED, float(limit), float(slope), float(offset)
+
+
+def expert_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor,
+                row_index: torch.Tensor | None, index_divisor: int = 1, gated=None) -> None:
+    """Rows in lists, a matrix per list: for list e (rows ``offsets[e]`` to ``offsets[e + 1]``) ``out[row] =
+    x[source(row)] @ w[e]^T``; ``source(row) = row_index[row] // index_divisor`` or, without an index,
+    the row itself.  ``w`` is ``[E, N, K]``; ``gated``: ``w`` is ``[E, 2 N, K]`` with the gate rows first and
+    ``out = act(gate) * up``: ``"silu"``, or ``("capped", limit, slope, offset)`` for ``g sigmoid(slope g) (u +
+    offset)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``."""
+    experts, wn, k = w.shape
+    list_rows, n = out.shape
+    kind, limit, slope, offset = _gate(gated)
+    if wn != (2 * n if kind else n):
+        raise KernelError(f"expert matrices {tuple(w.shape)} do not give {n} columns")
+    _run("grouped", "b200_grouped_gemm",
+         _P(_check("expert input", x, _RUN, (None, k))), _P(_check("expert matrices", w, x.dtype)),
+         _P(_check("expert output", out, x.dtype)), _P(_check("list offsets", offsets, torch.int32, (experts + 1,))),
+         _P(_check("row index", row_index, torch.int32, (list_rows,), optional=True)), _I(index_divisor), _I(0),
+         _I(list_rows), _I(experts), _I(n), _I(k), _L(k), _L(n), _L(0), _L(0), _I(kind), _F(limit), _F(slope),
+         _F(offset), _I(_code(x.dtype)), _stream())
+
+
+def head_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, column: int = 0) -> None:
+    """A matrix per head: rows of ``x`` hold the heads' inputs side by side (``K`` columns each, the first
+    at ``column`` of a possibly wider row), rows of ``out`` ``[T, H * N]`` their outputs: ``out[t, h] = x[t, h]
+    @ w[h]^T`` with ``w`` ``[H, N, K]``."""
+    heads, n, k = w.shape
+    tokens, stride = x.shape
+    if column < 0 or column + heads * k > stride:
+        raise KernelError(f"head inputs: columns {column} to {column + heads * k} of rows of {stride}")
+    _check("head inputs", x, _RUN)
+    _run("grouped", "b200_grouped_gemm",
+         _P(x.data_ptr() + column * x.element_size()), _P(_check("head matrices", w, x.dtype)),
+         _P(_check("head outputs", out, x.dtype, (tokens, heads * n))), _P(0), _P(0), _I(1), _I(tokens), _I(0),
+         _I(heads), _I(n), _I(k), _L(stride), _L(heads * n), _L(k), _L(n), _I(0), _F(0.0), _F(0.0), _F(0.0),
+         _I(_code(x.dtype)), _stream())
+
+
+def capped_swish_mul(gate_up: torch.Tensor, out: torch.Tensor, limit: float | None, slope: float,
+                     offset: float) -> None:
+    """``out = g * sigmoid(slope * g) * (u + offset)`` in float32 with ``g = min(gate_up[:, :I], limit)`` and
+    ``u = clamp(gate_up[:, I:], -limit, limit)`` (``limit`` None: no cap)."""
+    tokens, inter = out.shape
+    _run("grouped", "b200_capped_swish_mul", _P(_check("gate_up", gate_up, out.dtype, (tokens, 2 * inter))),
+         _P(_check("activation output", out, _RUN)), _I(tokens), _I(inter),
+         _F(math.inf if limit is None else limit), _F(slope), _F(offset), _I(_code(out.dtype)), _stream())
+
+
+def gelu_gate_rows(gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
+                   column: int) -> None:
+    """``out[t] = gelu_tanh(gate[t]) * table[ids[t], column : column + dim]`` in float32."""
+    tokens, dim = gate.shape
+    vocab, stride = table.shape
+    _run("grouped", "b200_gelu_gate_rows", _P(_check("gate rows", gate, _RUN)),
+         _P(_check("table", table, gate.dtype)), _P(_check("token ids", ids, torch.int32, (tokens,))),
+         _P(_check("gated rows", out, gate.dtype, (tokens, dim))), _I(tokens), _I(dim), _I(stride), _I(column),
+         _I(vocab), _I(_code(gate.dtype)), _stream())

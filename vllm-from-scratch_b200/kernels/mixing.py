@@ -16,22 +16,25 @@ _RUN = (torch.float32, torch.bfloat16)
 
 
 # ------------------------------------------------------------------------ norms
-def add_normed_rmsnorm(x: torch.Tensor, x_weight: torch.Tensor, x_eps: float, residual: torch.Tensor,
+def add_normed_rmsnorm(x: torch.Tensor | None, x_weight: torch.Tensor | None, x_eps: float, residual: torch.Tensor,
                        weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
                        rows: torch.Tensor | None = None) -> None:
-    """``residual += rms(x) * x_weight`` in float32, then ``out = rms(residual) * weight`` in
-    ``out``'s dtype (``weight`` and ``out`` both None: the sum only).  With ``rows`` only those rows
-    are formed, written compactly to ``out``, and ``residual`` is left as it was."""
+    """``residual += rms(x) * x_weight`` in float32 (skipped when ``x`` is None), then ``out =
+    rms(residual) * weight`` in ``out``'s dtype; ``weight`` None: ``out`` is the residual itself in
+    ``out``'s dtype (what a sublayer reads that has no norm in front of it); ``out`` None as well:
+    the sum only.  With ``rows`` only those rows are formed, written compactly to ``out``, and
+    ``residual`` is left as it was."""
     tokens, hidden = residual.shape
     out_rows = tokens if rows is None else rows.shape[0]
+    dtype = x.dtype if x is not None else out.dtype
     _run("norm_ext", "b200_add_normed_rmsnorm",
-         _P(_check("normed addend", x, _RUN, (tokens, hidden))),
-         _P(_check("addend norm weight", x_weight, torch.float32, (hidden,))), _F(x_eps),
+         _P(_check("normed addend", x, _RUN, (tokens, hidden), optional=True)),
+         _P(_check("addend norm weight", x_weight, torch.float32, (hidden,), optional=True)), _F(x_eps),
          _P(_check("residual", residual, torch.float32)),
          _P(_check("norm weight", weight, torch.float32, (hidden,), optional=True)),
-         _P(_check("norm output", out, x.dtype, (out_rows, hidden), optional=True)),
+         _P(_check("norm output", out, dtype, (out_rows, hidden), optional=True)),
          _P(_check("row index", rows, torch.int32, optional=True)),
-         _I(out_rows), _I(hidden), _F(eps), _I(_code(x.dtype)), _stream())
+         _I(out_rows), _I(hidden), _F(eps), _I(_code(dtype)), _stream())
 
 
 def paired_norm_mean(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, eps: float,
@@ -93,25 +96,38 @@ def head_norm_scale_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: tor
                           q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
                           temperature: tuple[float, int] | None, q_out: torch.Tensor,
                           k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, num_q_heads: int,
-                          num_kv_heads: int, head_dim: int, value_dim: int, page_size: int) -> None:
+                          num_kv_heads: int, head_dim: int, value_dim: int, page_size: int,
+                          unit_norm: bool = False, column: int = 0) -> None:
     """From the packed projection ``[T, nq d + nkv d + nkv dv]``: per-head RMSNorm of queries and
     keys, queries times ``1 + coef * ln(floor((p + 1) / every) + 1)`` for ``temperature = (coef,
-    every)``, queries to ``q_out``, keys and values to their pages at ``slots``."""
+    every)``, queries to ``q_out``, keys and values to their pages at ``slots``.
+
+    ``unit_norm``: queries and keys are divided by their root mean square also where no weight
+    vector is given (without it an absent weight means no norm).  ``value_dim = 0``: keys only, no
+    values are stored (``num_q_heads = 0`` with it: rows of keys alone are normalised into their
+    pages).  ``column``: the rows begin at that column of a wider ``qkv``."""
     tokens = qkv.shape[0]
     dtype = qkv.dtype
     width = (num_q_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim
     coef, every = temperature if temperature is not None else (0.0, 0)
+    stride = qkv.shape[1]
+    if column < 0 or column + width > stride:
+        from . import KernelError
+        raise KernelError(f"qkv: columns {column} to {column + width} of rows of {stride}")
+    _check("qkv", qkv, _RUN, (tokens, stride))
     _run("attention_bias", "b200_head_norm_scale_cache",
-         _P(_check("qkv", qkv, _RUN, (tokens, width))),
+         _P(qkv.data_ptr() + column * qkv.element_size()),
          _P(_check("positions", positions, torch.int32, (tokens,))),
          _P(_check("slot mapping", slots, torch.int32, (tokens,))),
          _P(_check("q head-norm weight", q_weight, torch.float32, (head_dim,), optional=True)),
          _P(_check("k head-norm weight", k_weight, torch.float32, (head_dim,), optional=True)),
-         _P(_check("q output", q_out, dtype, (tokens, num_q_heads * head_dim))),
+         _P(_check("q output", q_out, dtype, (tokens, num_q_heads * head_dim), optional=num_q_heads == 0)),
          _P(_check("key pages", k_pages, dtype, (None, num_kv_heads, page_size, head_dim), optional=True)),
-         _P(_check("value pages", v_pages, dtype, (None, num_kv_heads, page_size, value_dim), optional=True)),
+         _P(_check("value pages", v_pages, dtype, (None, num_kv_heads, page_size, value_dim), optional=True)
+            if value_dim else 0),
          _I(tokens), _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(value_dim), _I(page_size),
-         _F(eps), _F(coef), _I(every), _I(_code(dtype)), _stream())
+         _F(eps), _F(coef), _I(every), _I(stride), _I(1 if (unit_norm or q_weight is not None) else 0),
+         _I(1 if (unit_norm or k_weight is not None) else 0), _I(_code(dtype)), _stream())
 
 
 # Tests set this to False to drive the float32-arithmetic kernel through the same call.
@@ -132,9 +148,11 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                            slopes: torch.Tensor | None, num_q_heads: int, num_kv_heads: int, head_dim: int,
                            value_dim: int, page_size: int, scale: float, window: int | None,
                            max_query_len: int | None = None, max_seq_len: int | None = None,
-                           num_decode: int = 0) -> None:
+                           num_decode: int = 0, sinks: torch.Tensor | None = None) -> None:
     """Causal attention of every request's new queries over its pages with the score ``q . k * scale
-    - slopes[h] * (i - j)``; scores, weights and the weighted sum in float32.
+    - slopes[h] * (i - j)``; scores, weights and the weighted sum in float32.  ``sinks`` (float32, one
+    per query head): ``exp(sinks[h])`` joins the softmax denominator of head h once, unscaled, with no
+    key and no value.  ``v_pages`` may be ``k_pages`` itself (keys that serve as the values too).
 
     bfloat16 with keys and values of one size of 64, 128 or 256 (and ``max_query_len`` and
     ``max_seq_len`` given): the tensor-core kernels, whose softmax weights enter the second product
@@ -153,11 +171,12 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
         _check("query_start", query_start, torch.int32, (requests + 1,)),
         _check("seq_lens", seq_lens, torch.int32, (requests,)),
         _check("block table", block_table, torch.int32, (requests, None)),
-        _check("slopes", slopes, torch.float32, (num_q_heads,), optional=True))
+        _check("slopes", slopes, torch.float32, (num_q_heads,), optional=True),
+        _check("sinks", sinks, torch.float32, (num_q_heads,), optional=True))
     if (USE_TENSOR_CORES and dtype == torch.bfloat16 and max_query_len is not None and max_seq_len is not None
             and head_dim == value_dim and head_dim in (64, 128, 256) and num_q_heads // num_kv_heads <= 16):
         from .attention_bf16 import decode_splits
-        q_p, k_p, v_p, out_p, start_p, lens_p, table_p, slopes_p = checked
+        q_p, k_p, v_p, out_p, start_p, lens_p, table_p, slopes_p, sinks_p = checked
         single = requests if (max_query_len == 1 and tokens == requests) else num_decode
         width = block_table.shape[1]
         if single > 0:
@@ -168,7 +187,7 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                 partial_ml = torch.empty((single * num_q_heads * splits, 2), dtype=torch.float32, device=q.device)
             _run("attention_bias", "b200_biased_decode_attention_bf16", _P(q_p), _P(k_p), _P(v_p), _P(out_p),
                  _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
-                 _P(lens_p), _P(table_p), _P(slopes_p), _I(single), _I(width), _I(num_q_heads), _I(num_kv_heads),
+                 _P(lens_p), _P(table_p), _P(slopes_p), _P(sinks_p), _I(single), _I(width), _I(num_q_heads), _I(num_kv_heads),
                  _I(head_dim), _I(page_size), _F(scale), _I(window or 0), _I(splits), _stream())
             if splits > 1:
                 count_launch()
@@ -177,6 +196,7 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
             # the batch's own q, out and query_start (rows of the whole batch).
             _run("attention_bias", "b200_biased_prefill_attention_bf16", _P(q_p), _P(k_p), _P(v_p), _P(out_p),
                  _P(start_p + 4 * single), _P(lens_p + 4 * single), _P(table_p + 4 * single * width), _P(slopes_p),
+                 _P(sinks_p),
                  _I(requests - single), _I(tokens), _I(width), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
                  _I(page_size), _F(scale), _I(window or 0), _I(single), _stream())
         return

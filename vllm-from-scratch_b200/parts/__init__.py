@@ -1,9 +1,9 @@
 """Parts a model is put together from, and the model assembled from them."""
 
-from . import attention, block, embedding, feed_forward, norm, paired, position, recurrent  # noqa: F401  (register the built-in kinds)
-from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, OUTPUT_HEADS, POSITION_ENCODINGS, Block,
+from . import attention, block, embedding, feed_forward, latent, norm, paired, position, recurrent, side  # noqa: F401  (register the built-in kinds)
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, OUTPUT_HEADS, POSITION_ENCODINGS, TOKEN_SIDES, Block,
                    CacheView, Embedding, FeedForward, GroupContext, KVPagesNeed, Mixer, Norm, OutputHead, Part,
-                   NormedAddend, PartEnv, PositionEncoding, StateNeed, StepContext, WeightInfo)
+                   NormedAddend, PartEnv, PositionEncoding, StateNeed, StepContext, TokenSide, WeightInfo)
 from .model import DecoderModel
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
@@ -11,5 +11,5 @@ __all__ = [
     "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "MIXERS", "NORMS", "OUTPUT_HEADS", "POSITION_ENCODINGS", "Block",
     "CacheView", "DecoderModel", "Embedding", "FeedForward", "GroupContext", "KVPagesNeed", "LayerSpec", "Mixer", "ModelSpec",
     "Norm", "NormedAddend", "OutputHead", "Part", "PartEnv", "PartSpec", "PositionEncoding", "ScheduleEntry", "StateNeed",
-    "StepContext", "WeightInfo",
+    "StepContext", "TOKEN_SIDES", "TokenSide", "WeightInfo",
 ]

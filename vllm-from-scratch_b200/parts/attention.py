@@ -142,7 +142,10 @@ class BiasedAttention(Mixer):
 
     params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``value_dim`` (default ``head_dim``),
     ``scale``, ``slopes`` (one per head, or None for no bias), ``window`` (None = all keys),
-    ``qk_norm_eps`` (None = no head norm), ``q_temperature`` (``(coef, every)`` or None),
+    ``qk_norm_eps`` (None = no head norm), ``qk_norm_weights`` (default True; False: queries and keys are
+    divided by their root mean square and nothing else, the checkpoint has no vectors for it),
+    ``q_temperature`` (``(coef, every)`` or None), ``cache_window`` (positions the cache keeps, where
+    another layer reads it over a longer window than this one's; default: the window),
     ``weight_names`` (q, k, v, o matrices, q and k norm vectors)."""
 
     graph_safe = True
@@ -160,6 +163,8 @@ class BiasedAttention(Mixer):
         self.window = None if window is None else int(window)
         eps = params.get("qk_norm_eps")
         self.qk_norm_eps = None if eps is None else float(eps)
+        self.qk_norm_weights = bool(params.get("qk_norm_weights", True))
+        self.cache_window = params.get("cache_window", self.window)
         temperature = params.get("q_temperature")
         self.q_temperature = None if temperature is None else (float(temperature[0]), int(temperature[1]))
         slopes = params.get("slopes")
@@ -183,7 +188,7 @@ class BiasedAttention(Mixer):
         q, k, v, o, qn, kn = self.names
         names = {q: WeightInfo((self.num_heads * d, hidden)), k: WeightInfo((self.num_kv_heads * d, hidden)),
                  v: WeightInfo((self.num_kv_heads * dv, hidden)), o: WeightInfo((hidden, self.num_heads * dv))}
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weights:
             names[qn] = WeightInfo((d,), "vector")
             names[kn] = WeightInfo((d,), "vector")
         return names
@@ -192,11 +197,11 @@ class BiasedAttention(Mixer):
         q, k, v, o, qn, kn = self.names
         self.qkv = torch.cat([tensors[q], tensors[k], tensors[v]], dim=0).contiguous()
         self.out_proj = tensors[o].contiguous()
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weights:
             self.q_norm, self.k_norm = tensors[qn], tensors[kn]
 
     def cache_need(self) -> KVPagesNeed:
-        return KVPagesNeed(self.num_kv_heads, self.head_dim, self.window, self.value_dim)
+        return KVPagesNeed(self.num_kv_heads, self.head_dim, self.cache_window, self.value_dim)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         if cache.kind != "pages":
@@ -211,7 +216,7 @@ class BiasedAttention(Mixer):
         kernels.head_norm_scale_cache(
             qkv, ctx.positions, group.slot_mapping, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0,
             self.q_temperature, q, cache.keys if store else None, cache.values if store else None, nq, nkv, d, dv,
-            group.page_size)
+            group.page_size, unit_norm=self.qk_norm_eps is not None and not self.qk_norm_weights)
         attended = torch.empty((tokens, nq * dv), dtype=x.dtype, device=x.device)
         kernels.biased_paged_attention(
             q, cache.keys, cache.values, attended, ctx.query_start, ctx.seq_lens, group.block_table, self.slopes,

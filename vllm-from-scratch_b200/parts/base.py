@@ -48,7 +48,8 @@ class KVPagesNeed:
     head_dim: int
     window: int | None = None
     # Size of a value head where it differs from the keys' (None: the same).  Keys and values
-    # then live in slabs of their own.
+    # then live in slabs of their own.  0: no values are kept at all, the cached rows serve as
+    # keys and as values (``CacheView.values`` is then ``CacheView.keys``).
     value_dim: int | None = None
 
 
@@ -95,6 +96,8 @@ class StepContext:
     # In a step that mixes them, the first num_decode requests bring one token each and the
     # others portions of prompts; 0 in a step of one kind (and for code that does not care).
     num_decode: int = 0
+    # int32 [T] the tokens themselves, for parts behind the embedding that look a token up again.
+    token_ids: torch.Tensor | None = None
 
 
 @dataclass
@@ -226,6 +229,16 @@ class FeedForward(Part):
         return False
 
 
+class TokenSide(Part):
+    """What a layer adds for the token itself, behind its sublayers: rows made from the residual
+    stream and from the token ids (a row of a table per token, for instance).  params always hold
+    ``vocab_size``."""
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """``x`` is ``[T, hidden]`` in the run dtype, ``ctx.token_ids`` the tokens; returns ``[T, hidden]``."""
+        raise NotImplementedError
+
+
 class Embedding(Part):
     """From token ids to the first content of the float32 residual stream.  params always
     hold ``vocab_size``.  ``table()`` is the ``[vocab, hidden]`` matrix an output head that
@@ -269,10 +282,15 @@ class Block(Part):
 
     norm_roles: tuple[str, ...] = ()
     needs_feed_forward: bool = True
+    takes_side: bool = False            # whether the arrangement has a place for a :class:`TokenSide`
 
     def __init__(self, params: Mapping[str, Any], env: PartEnv, *, mixer: Mixer,
-                 feed_forward: FeedForward | None, norms: Mapping[str, Norm]) -> None:
+                 feed_forward: FeedForward | None, norms: Mapping[str, Norm],
+                 side: "TokenSide | None" = None) -> None:
         super().__init__(params, env)
+        if side is not None and not self.takes_side:
+            raise ValueError(f"block at {env.prefix!r} has no place for a token side")
+        self.side = side
         if set(norms) != set(self.norm_roles):
             raise ValueError(f"block at {env.prefix!r} arranges norms {sorted(self.norm_roles)}, "
                              f"the layer brings {sorted(norms)}")
@@ -338,4 +356,5 @@ NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
+TOKEN_SIDES = Registry("token side")
 OUTPUT_HEADS = Registry("output head")

@@ -14,7 +14,8 @@ from __future__ import annotations
 
 import torch
 
-from .base import BLOCKS, Block, CacheView, HalfNormedRows, Norm, StepContext  # noqa: F401
+from .. import kernels
+from .base import BLOCKS, Block, CacheView, HalfNormedRows, Norm, NormedAddend, StepContext  # noqa: F401
 
 
 @BLOCKS.register("pre_norm")
@@ -74,3 +75,54 @@ class SandwichNormBlock(Block):
             return mixed
         normed = self.norms["feed_forward"].forward(mixed, residual)
         return self.norms["post_feed_forward"].addend(self.feed_forward.forward(normed, ctx))
+
+
+@BLOCKS.register("post_norm")
+class PostNormBlock(Block):
+    """A norm behind each sublayer and none in front: ``h += post_mixer(mixer(h))``, then, where the layer
+    has one, ``h += post_feed_forward(feed_forward(h))``, then, where the layer has one, ``h +=
+    post_side(side(h, tokens))``.  Every sublayer reads the residual stream itself (in the run dtype).
+
+    What a sublayer returns travels on as a :class:`~.base.NormedAddend`; the kernel that normalises it and
+    adds it into the float32 residual also writes the sum in the run dtype, which the next sublayer (the next
+    layer's mixer) reads.  In the float32 run mode the sublayers read the residual in place."""
+
+    graph_safe = True
+    needs_feed_forward = False
+    takes_side = True
+
+    def __init__(self, params, env, *, mixer, feed_forward, norms, side=None) -> None:
+        roles = ["post_mixer"]
+        if feed_forward is not None:
+            roles.append("post_feed_forward")
+        if side is not None:
+            roles.append("post_side")
+        self.norm_roles = tuple(roles)
+        super().__init__(params, env, mixer=mixer, feed_forward=feed_forward, norms=norms, side=side)
+        for role, norm in self.norms.items():
+            if not hasattr(norm, "addend"):
+                raise ValueError(f"block at {env.prefix!r}: the norm behind a sublayer ({role}) must be able to "
+                                 f"travel with its rows (an `addend` method)")
+
+    def _rows(self, pending: NormedAddend | None, residual: torch.Tensor) -> torch.Tensor:
+        """Add what is pending into the residual and return the stream as the next sublayer reads it."""
+        if pending is not None and not isinstance(pending, NormedAddend):
+            raise ValueError("a post-norm block takes what is handed to it as rows under the norm behind them")
+        addend = (None, None, 0.0) if pending is None else (pending.rows, pending.weight, pending.eps)
+        if self.env.dtype == torch.float32:
+            if pending is not None:
+                kernels.add_normed_rmsnorm(*addend, residual, None, 0.0, None)
+            return residual
+        rows = torch.empty(residual.shape, dtype=self.env.dtype, device=residual.device)
+        kernels.add_normed_rmsnorm(*addend, residual, None, 0.0, rows)
+        return rows
+
+    def forward(self, x, residual: torch.Tensor, ctx: StepContext, cache: CacheView) -> NormedAddend:
+        pending = self.norms["post_mixer"].addend(self.mixer.forward(self._rows(x, residual), ctx, cache))
+        if self.feed_forward is not None:
+            rows = self._rows(pending, residual)
+            pending = self.norms["post_feed_forward"].addend(self.feed_forward.forward(rows, ctx))
+        if self.side is not None:
+            rows = self._rows(pending, residual)
+            pending = self.norms["post_side"].addend(self.side.forward(rows, ctx))
+        return pending

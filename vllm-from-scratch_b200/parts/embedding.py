@@ -21,20 +21,21 @@ from .base import (EMBEDDINGS, OUTPUT_HEADS, CacheView, Embedding, OutputHead, P
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: ``vocab_size``."""
+    """params: ``vocab_size``; ``weight_name`` (default ``weight``)."""
 
     graph_safe = True
 
     def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
         super().__init__(params, env)
         self.vocab_size = int(params["vocab_size"])
+        self.weight_name = str(params.get("weight_name", "weight"))
         self.weight: torch.Tensor | None = None
 
     def expected_weights(self) -> dict[str, WeightInfo]:
-        return {"weight": WeightInfo((self.vocab_size, self.env.hidden_size))}
+        return {self.weight_name: WeightInfo((self.vocab_size, self.env.hidden_size))}
 
     def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.weight_name].contiguous()
 
     def forward(self, token_ids: torch.Tensor, ctx: StepContext, residual: torch.Tensor,
                 error_flag: torch.Tensor) -> None:

@@ -58,3 +58,132 @@ class GatedSiluFeedForward(FeedForward):
         squares = torch.empty((tokens, self.env.hidden_size // 8), dtype=torch.float32, device=x.device)
         kernels.gemm(hidden, self.down, out, fold=(residual, weight, squares))
         return HalfNormedRows(out, squares, eps)
+
+
+@FEED_FORWARDS.register("capped_gated")
+class CappedGatedFeedForward(FeedForward):
+    """``down(g * sigmoid(slope * g) * (u + up_offset))`` with ``g = min(gate(x), limit)`` and ``u = clamp(up(x),
+    -limit, limit)``; the activation in float32.
+
+    params: ``intermediate_size``, ``limit`` (None: no cap), ``slope`` (default 1.702), ``up_offset`` (default 1),
+    ``weight_names`` (gate, up, down; default ``gate``, ``up``, ``down``)."""
+
+    graph_safe = True
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
+        super().__init__(params, env)
+        self.intermediate_size = int(params["intermediate_size"])
+        limit = params.get("limit")
+        self.limit = None if limit is None else float(limit)
+        self.slope = float(params.get("slope", 1.702))
+        self.up_offset = float(params.get("up_offset", 1.0))
+        self.names = tuple(params.get("weight_names", ("gate", "up", "down")))
+        self.gate_up: torch.Tensor | None = None
+        self.down: torch.Tensor | None = None
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        inter, hidden = self.intermediate_size, self.env.hidden_size
+        gate, up, down = self.names
+        return {gate: WeightInfo((inter, hidden)), up: WeightInfo((inter, hidden)), down: WeightInfo((hidden, inter))}
+
+    def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        gate, up, down = self.names
+        self.gate_up = torch.cat([tensors[gate], tensors[up]], dim=0).contiguous()
+        self.down = tensors[down].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        from ..kernels import grouped
+        tokens = x.shape[0]
+        gate_up = torch.empty((tokens, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.gemm(x, self.gate_up, gate_up)
+        hidden = torch.empty((tokens, self.intermediate_size), dtype=x.dtype, device=x.device)
+        grouped.capped_swish_mul(gate_up, hidden, self.limit, self.slope, self.up_offset)
+        out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
+        kernels.gemm(hidden, self.down, out)
+        return out
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    """A mixture of small gated feed-forwards, ``down_e(silu(gate_e x) * up_e x)``, of which every token uses
+    ``top``: router logits in float32, scores = sigmoid(logits); the choice is made on ``score + correction``
+    (where the checkpoint has a correction), among the experts of the ``group_keep`` best of ``group_count``
+    equal groups of neighbouring experts (a group's mark is the sum of its ``group_top`` largest choice
+    scores); the output is the sum of the chosen experts' outputs weighted with their plain scores, not
+    renormalised.
+
+    The tokens of a step are put into one list per expert on the device, the experts' products run as two
+    grouped kernels over those lists (the first with the activation in its epilogue), and a last kernel adds
+    every token's rows in the order of its choices: nothing depends on host values, whatever the routing.
+
+    params: ``num_experts``, ``top``, ``intermediate_size``, ``group_count`` (default 1), ``group_keep``
+    (default ``group_count``), ``group_top`` (default 2), ``correction`` (default True), ``router_name``
+    (default ``router``), ``correction_name`` (default ``correction``), ``expert_names`` (patterns with
+    ``{index}`` for gate, up, down; default ``e{index}.gate``, ``e{index}.up``, ``e{index}.down``)."""
+
+    graph_safe = True
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
+        super().__init__(params, env)
+        self.num_experts = int(params["num_experts"])
+        self.top = int(params["top"])
+        self.intermediate_size = int(params["intermediate_size"])
+        self.group_count = int(params.get("group_count", 1))
+        self.group_keep = int(params.get("group_keep", self.group_count))
+        self.group_top = int(params.get("group_top", 2))
+        self.has_correction = bool(params.get("correction", True))
+        self.router_name = str(params.get("router_name", "router"))
+        self.correction_name = str(params.get("correction_name", "correction"))
+        self.expert_names = tuple(params.get("expert_names", ("e{index}.gate", "e{index}.up", "e{index}.down")))
+        if not 1 <= self.top <= self.num_experts:
+            raise ValueError(f"top={self.top} of {self.num_experts} experts")
+        if self.group_count < 1 or self.num_experts % self.group_count:
+            raise ValueError(f"{self.num_experts} experts do not form {self.group_count} equal groups")
+        if not 1 <= self.group_keep <= self.group_count:
+            raise ValueError(f"group_keep={self.group_keep} of {self.group_count} groups")
+        if self.top > self.group_keep * (self.num_experts // self.group_count):
+            raise ValueError(f"top={self.top} experts cannot come from {self.group_keep} groups of "
+                             f"{self.num_experts // self.group_count}")
+        self.router = self.correction = self.gate_up = self.down = None
+
+    def _expert(self, index: int) -> tuple[str, str, str]:
+        return tuple(pattern.format(index=index) for pattern in self.expert_names)
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        inter, hidden = self.intermediate_size, self.env.hidden_size
+        # the router's matrix is used in 32-bit arithmetic: kept in float32 like a norm's vector
+        names = {self.router_name: WeightInfo((self.num_experts, hidden), "vector")}
+        if self.has_correction:
+            names[self.correction_name] = WeightInfo((self.num_experts,), "vector")
+        for index in range(self.num_experts):
+            gate, up, down = self._expert(index)
+            names[gate] = WeightInfo((inter, hidden))
+            names[up] = WeightInfo((inter, hidden))
+            names[down] = WeightInfo((hidden, inter))
+        return names
+
+    def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.router = tensors[self.router_name].contiguous()
+        self.correction = tensors[self.correction_name].contiguous() if self.has_correction else None
+        names = [self._expert(index) for index in range(self.num_experts)]
+        self.gate_up = torch.stack([torch.cat([tensors[gate], tensors[up]], dim=0) for gate, up, _ in names]).contiguous()
+        self.down = torch.stack([tensors[down] for _, _, down in names]).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        from ..kernels import grouped
+        tokens, device = x.shape[0], x.device
+        top, experts = self.top, self.num_experts
+        ids = torch.empty((tokens, top), dtype=torch.int32, device=device)
+        weights = torch.empty((tokens, top), dtype=torch.float32, device=device)
+        grouped.route_experts(x, self.router, self.correction, ids, weights, top, self.group_count,
+                              self.group_keep, self.group_top)
+        books = torch.empty(experts + 1 + 2 * tokens * top, dtype=torch.int32, device=device)
+        offsets, sorted_pair, position = torch.split(books, [experts + 1, tokens * top, tokens * top])
+        grouped.expert_lists(ids, experts, offsets, sorted_pair, position)
+        hidden = torch.empty((tokens * top, self.intermediate_size), dtype=x.dtype, device=device)
+        grouped.expert_gemm(x, self.gate_up, hidden, offsets, sorted_pair, top, gated="silu")
+        rows = torch.empty((tokens * top, self.env.hidden_size), dtype=x.dtype, device=device)
+        grouped.expert_gemm(hidden, self.down, rows, offsets, None)
+        out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=device)
+        grouped.combine_experts(rows, position, weights, out)
+        return out

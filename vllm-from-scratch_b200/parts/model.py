@@ -15,12 +15,16 @@ from typing import Mapping
 import torch
 
 from .. import kernels
-from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, OUTPUT_HEADS, POSITION_ENCODINGS, Block,
-                   CacheView, KVPagesNeed, PartEnv, StateNeed, StepContext, WeightInfo)
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, OUTPUT_HEADS, POSITION_ENCODINGS, TOKEN_SIDES,
+                   Block, CacheView, KVPagesNeed, PartEnv, StateNeed, StepContext, WeightInfo)
 from .spec import LayerSpec, ModelSpec
 
 
 def _join(prefix: str, name: str) -> str:
+    # A name that begins with "/" is the tensor's whole name: a tensor that several parts share
+    # (a table of which every layer reads its columns) lies outside any one part's prefix.
+    if name.startswith("/"):
+        return name[1:]
     return f"{prefix}.{name}" if prefix and name else prefix or name
 
 
@@ -57,8 +61,12 @@ class DecoderModel:
         if layer.feed_forward is not None:
             feed_forward = FEED_FORWARDS.get(layer.feed_forward.kind)(
                 layer.feed_forward.params, env(layer.feed_forward))
+        extra = {}
+        if layer.side is not None:
+            extra["side"] = TOKEN_SIDES.get(layer.side.kind)(
+                {"vocab_size": self.vocab_size, **layer.side.params}, env(layer.side))
         return BLOCKS.get(layer.block.kind)(
-            layer.block.params, env(layer.block), mixer=mixer, feed_forward=feed_forward, norms=norms)
+            layer.block.params, env(layer.block), mixer=mixer, feed_forward=feed_forward, norms=norms, **extra)
 
     def _parts(self):
         yield self.embedding
@@ -66,6 +74,8 @@ class DecoderModel:
             yield from (block, block.mixer, block.mixer.position, *block.norms.values())
             if block.feed_forward is not None:
                 yield block.feed_forward
+            if getattr(block, "side", None) is not None:
+                yield block.side
         yield from (self.final_norm, self.output_head)
 
     def graph_safe(self) -> bool:
@@ -136,6 +146,7 @@ class DecoderModel:
         receives ``(x, residual copy)`` after every layer execution, for looking inside."""
         tokens = token_ids.shape[0]
         residual = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=token_ids.device)
+        ctx.token_ids = token_ids
         if embedding_cache is not None:
             self.embedding.forward(token_ids, ctx, residual, self._token_error, cache=embedding_cache)
         else:

@@ -49,13 +49,14 @@ class LayerSpec:
     feed_forward: PartSpec | None     # dense or experts
     position: PartSpec                # position encoding handed to the mixer
     norms: Mapping[str, PartSpec] = field(default_factory=dict)
+    side: PartSpec | None = None      # what the layer adds for the token itself, if anything
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "norms", MappingProxyType(dict(self.norms)))
 
     def __hash__(self) -> int:
         return hash((self.name, self.block, self.mixer, self.feed_forward, self.position,
-                     tuple(sorted(self.norms.items()))))
+                     tuple(sorted(self.norms.items())), self.side))
 
 
 @dataclass(frozen=True)
