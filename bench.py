@@ -547,6 +547,36 @@ def _bemuzen(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> di
             "layers": [scan if index % 4 == 1 else parallel for index in range(layers)]}
 
 
+def _lobuzen(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> dict:
+    """Layers of the sizes of a Qwen3 layer of this width.  Attention layers have the Qwen3 layer's heads
+    (8 key/value heads of 128) and a window of 1024; latent layers as many heads over cached rows of 256 with a
+    window of 2048, the third layer reading the second's rows.  The first layer's feed-forward is dense with the
+    Qwen3 layer's width; the others route every token to 2 of 8 experts of half that width (4 groups, 2 kept), so
+    that a token passes through as many feed-forward parameters as in the Qwen3 layer.  A token side of 64."""
+    dense = {"kind": "dense", "ff": inter, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": inter // 2},
+           "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
+
+    def attention(mlp):
+        return {"type": "attention", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128,
+                                                            "scale": 128 ** -0.5, "mask": {"size": 1024}}}
+
+    def latent(mlp, kv_from=None):
+        mixer = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 256, "scale": 128 ** -0.5, "mask": {"size": 2048}}
+        if kv_from is not None:
+            mixer["kv_from"] = kv_from
+        return {"type": "latent_attention", "mlp": mlp, "mixer": mixer}
+
+    made = []
+    for index in range(layers):
+        place = index % 4
+        made.append(attention(dense) if place == 0 else latent(moe) if place == 1
+                    else latent(moe, kv_from=index - 1) if place == 2 else attention(moe))
+    return {"architecture": "Lobuzen", "vocab": vocab, "width": hidden, "norm": {"eps": 1e-6},
+            "token_side": {"dim": 64}, "layers": made}
+
+
+DESIGNS = {"bemuzen": _bemuzen, "lobuzen": _lobuzen}
 DESIGN_SIZES = {      # name -> (hidden, heads, feed-forward width)
     "1.7b-layers": (2048, 16, 6144),
     "8b-layers": (4096, 32, 12288),
@@ -590,15 +620,16 @@ def measure_prompt_steps(runner, config, tokens: int) -> dict:
 
 
 def run_design(args, measured, peak_kind) -> dict:
-    """``--design bemuzen``: prompt steps and decode steps of Bemuzen layers beside Qwen3 layers of the
+    """``--design NAME``: prompt steps and decode steps of that design's layers beside Qwen3 layers of the
     same width, heads, feed-forward, number of layers and vocabulary (random weights, bfloat16)."""
     import torch
     layers, vocab, context = args.layers or 4, 32768, args.context or 4096
+    design, title = args.design, args.design.capitalize()
     points = {}
     with ClockSampler() as clocks:
         for name, (hidden, heads, inter) in DESIGN_SIZES.items():
             qwen = dict(_qwen3(layers, hidden, heads, inter, False), vocab_size=vocab)
-            for label, raw in (("bemuzen", _bemuzen(layers, hidden, heads, inter, vocab)), ("qwen3", qwen)):
+            for label, raw in ((design, DESIGNS[design](layers, hidden, heads, inter, vocab)), ("qwen3", qwen)):
                 most = max(64 * (args.prompt_len + 600 + args.block_size), 8192 + 64)
                 runner, config = build_runner(raw, 64, most, args.block_size)
                 fill_cache_randomly(runner)
@@ -614,12 +645,12 @@ def run_design(args, measured, peak_kind) -> dict:
                 print(f"[bench] {name}/{label}: {json.dumps(entry)}", file=sys.stderr, flush=True)
                 del runner
                 torch.cuda.empty_cache()
-    main_point = points["1.7b-layers/bemuzen"]["decode_b8"]
+    main_point = points[f"1.7b-layers/{design}"]["decode_b8"]
     return {"metric": "decode_tokens_per_s_design", "value": main_point["tok_s"], "unit": "tokens/s", "n_gpus": 1,
             "steps": main_point["steps_timed"], "warmup": args.warmup, "ms_per_step": main_point["ms"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (random weights, random token ids)",
-            "config": {"model": f"Bemuzen layers beside Qwen3 layers, {layers} layers each", "global_batch": 8,
+            "config": {"model": f"{title} layers beside Qwen3 layers, {layers} layers each", "global_batch": 8,
                        "seq_len": args.prompt_len, "parallelism": "single GPU", "vocab": vocab,
                        "l2": "weights and cache exceed L2 (126 MB) at every size"},
             "clocks": clocks.summary(), "peaks": {**measured, "kind": peak_kind}, "design": points}
@@ -811,7 +842,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in config)")
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--no-points", action="store_true", help="the main point only")
-    parser.add_argument("--design", default=None, choices=("bemuzen",),
+    parser.add_argument("--design", default=None, choices=("bemuzen", "lobuzen"),
                         help="instead of the default workload: layers of this design beside Qwen3 layers of equal sizes")
     args = parser.parse_args()
 

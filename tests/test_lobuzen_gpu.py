@@ -20,12 +20,31 @@ CONFIGS, LENGTHS = lobuzen_configs.CONFIGS, lobuzen_configs.LENGTHS
 F32_REL, BF16_REL = 2e-5, 0.06
 
 
+def steady_choice(weights, raw):
+    """Corrections two apart from expert to expert, in a shuffled order of their own in every layer: no
+    sigmoid can bridge that, so the choice of experts never hangs on a close call between two scores,
+    while the weights of the chosen still differ from token to token."""
+    generator = torch.Generator().manual_seed(99)
+    for name, tensor in weights.items():
+        if name.endswith(".correction"):
+            levels = 2.0 * torch.randperm(tensor.shape[0], generator=generator).float() - tensor.shape[0]
+            weights[name] = levels.to(tensor.dtype)
+
+
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
-    # Stored in bfloat16: both run modes and the plain implementation then read the same numbers.
-    base = tmp_path_factory.mktemp("lobuzen")
-    return {name: helpers.make_model_folder(base, raw, seed=21 + i, dtype=torch.bfloat16)
-            for i, (name, (raw, _)) in enumerate(CONFIGS.items())}
+    """Stored in bfloat16: both run modes and the plain implementation then read the same numbers.  The
+    float32 runs route as the random weights say.  The bfloat16 runs get models whose choice of experts
+    is steady (``steady_choice``): the rounding of the stream moves a router's scores by about a
+    hundredth, which in a random model turns a close call the other way every few dozen tokens and
+    changes that row by far more than rounding."""
+    made = {}
+    for i, (name, (raw, _)) in enumerate(CONFIGS.items()):
+        made[name, "float32"] = helpers.make_model_folder(tmp_path_factory.mktemp("lobuzen"), raw, seed=21 + i,
+                                                          dtype=torch.bfloat16)
+        made[name, "bfloat16"] = helpers.make_model_folder(tmp_path_factory.mktemp("lobuzen_steady"), raw, seed=21 + i,
+                                                           dtype=torch.bfloat16, special=steady_choice)
+    return made
 
 
 def load_plain(folder, raw):
@@ -40,12 +59,12 @@ def load_plain(folder, raw):
 @pytest.fixture(scope="module")
 def references(folders):
     out = {}
-    for name, folder in folders.items():
+    for (name, dtype), folder in folders.items():
         raw = CONFIGS[name][0]
         model = load_plain(folder, raw)
         sequences = {rid: helpers.random_tokens(raw["vocab"], n, seed=sum(map(ord, name + rid)))
                      for rid, n in LENGTHS[name].items()}
-        out[name] = (sequences, {rid: model.run(rid, tokens).float() for rid, tokens in sequences.items()})
+        out[name, dtype] = (sequences, {rid: model.run(rid, tokens).float() for rid, tokens in sequences.items()})
     return out
 
 
@@ -85,11 +104,11 @@ def test_each_request_alone(folders, references, name, cut, dtype):
     """Whole prompts, prompts whose last 40 tokens are decoded one by one (every window passes over decoded
     tokens), portions of changing sizes down to two tokens, and whole sequences decoded token by token."""
     raw, page_size = CONFIGS[name]
-    sequences, expected = references[name]
+    sequences, expected = references[name, dtype]
     steps = CUTS[cut](LENGTHS[name])
     used = {rid for step in steps for rid, _ in step}
     longest = max(LENGTHS[name].values())
-    runner = make_runner(folders[name], dtype, page_size, -(-longest // page_size) + 1)
+    runner = make_runner(folders[name, dtype], dtype, page_size, -(-longest // page_size) + 1)
     results = helpers.run_schedule(runner, {rid: sequences[rid] for rid in used}, steps)
     compare(results, expected, dtype, f"{name}/{cut}/{dtype}")
     runner.check_device()
@@ -104,10 +123,10 @@ def test_mixed_batches_with_few_pages_and_slots(folders, references, name, seed,
     and a pool so small that the pages of a finished request are handed out again at once (windowed groups
     also give pages back while a request runs, and readers of another layer's rows find them in its pages)."""
     raw, page_size = CONFIGS[name]
-    sequences, expected = references[name]
+    sequences, expected = references[name, dtype]
     steps = helpers.cut_mixed(LENGTHS[name], seed=seed, live=3, sizes=(2, 3, 5, 8, 13, 16, 21, 33, 70))
     pages = sum(sorted((-(-n // page_size) for n in LENGTHS[name].values()), reverse=True)[:3])
-    runner = make_runner(folders[name], dtype, page_size, pages, max_requests=3)
+    runner = make_runner(folders[name, dtype], dtype, page_size, pages, max_requests=3)
     results = helpers.run_schedule(runner, sequences, steps)
     compare(results, expected, dtype, f"{name}/mixed{seed}/{dtype}")
     assert runner.manager.stats()["requests"] == 0
@@ -117,8 +136,8 @@ def test_long_decoding(folders, references):
     """A short prompt and 220 tokens decoded one by one: every window moves over decoded tokens only, and
     the windowed groups give back the pages behind them."""
     raw, page_size = CONFIGS["D"]
-    sequences, expected = references["D"]
-    runner = make_runner(folders["D"], "float32", page_size, 5)
+    sequences, expected = references["D", "float32"]
+    runner = make_runner(folders["D", "float32"], "float32", page_size, 5)
     steps = [[("g", 10)]] + [[("g", 1)] for _ in range(220)]
     results = helpers.run_schedule(runner, {"g": sequences["g"]}, steps)
     compare(results, expected, "float32", "D/long decode")
@@ -132,10 +151,10 @@ def test_greedy_generation_through_the_engine(folders, name, dtype):
     the token budget and run side by side."""
     import vllm_from_scratch_b200 as engine
     raw, page_size = CONFIGS[name]
-    model = load_plain(folders[name], raw)
+    model = load_plain(folders[name, dtype], raw)
     prompts = [helpers.random_tokens(raw["vocab"], n, seed=40 + n) for n in (5, 37, 1, 60)]
     new_tokens = 12
-    llm = engine.LLM(str(folders[name]), dtype=dtype, max_model_len=128, block_size=page_size, num_gpu_blocks=40,
+    llm = engine.LLM(str(folders[name, dtype]), dtype=dtype, max_model_len=128, block_size=page_size, num_gpu_blocks=40,
                      max_num_seqs=3, max_num_batched_tokens=24)
     outputs = llm.generate(prompts, engine.SamplingParams(max_tokens=new_tokens, temperature=0.0, ignore_eos=True))
     assert llm.engine.decode_graphs is not None and llm.engine.decode_graphs.replays > 0
@@ -162,7 +181,7 @@ def test_preempted_requests_are_computed_again(folders):
     params = engine.SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
     results = {}
     for label, blocks in (("large", 64), ("small", 8)):
-        llm = engine.LLM(str(folders["A"]), dtype="float32", max_model_len=128, block_size=page_size,
+        llm = engine.LLM(str(folders["A", "float32"]), dtype="float32", max_model_len=128, block_size=page_size,
                          num_gpu_blocks=blocks, max_num_seqs=4, max_num_batched_tokens=64)
         results[label] = llm.generate(prompts, params)
         if label == "small":

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
     const int* __restrict__ seq_lens, const int* __restrict__ block_table, int max_pages, int nq,
     int nkv, int page_size, float scale_log2, int window, int splits, const float* __restrict__ slopes,
-    const float* __restrict__ sinks) {
+    const float* __restrict__ sinks, int cache_nkv) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);
     overlap_trigger();
@@ -163,6 +163,9 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     const int split = blockIdx.x, kv_head = blockIdx.y, request = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int group = nq / nkv;
+    // The pages may hold fewer heads than the launch has key/value heads: query heads in more groups
+    // than there are cached heads, several groups reading the same rows (cache_nkv divides nkv).
+    const int cache_head = kv_head / (nkv / cache_nkv);
     const int seq_len = seq_lens[request];
     const int k_first = window > 0 ? max(0, seq_len - window) : 0;
     const int total = seq_len - k_first;
@@ -195,14 +198,14 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     auto v_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D + kKeys * D; };
 
     if (tiles > 0) {
-        load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, my_begin, my_end, kv_head, nkv, page_size, page_shift);
+        load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, my_begin, my_end, cache_head, cache_nkv, page_size, page_shift);
         cp_async_commit();
     }
     for (int t = 0; t < tiles; ++t) {
         const int k0 = my_begin + t * kKeys;
         if (t + 1 < tiles) {
             load_kv_tile<D>(k_stage((t + 1) & 1), v_stage((t + 1) & 1), k_pages, v_pages, table,
-                            k0 + kKeys, my_end, kv_head, nkv, page_size, page_shift);
+                            k0 + kKeys, my_end, cache_head, cache_nkv, page_size, page_shift);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -402,7 +405,7 @@ __global__ void __launch_bounds__(kThreads, EXACT ? 2 : 3) prefill_attention_ker
     bf16* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, int num_requests, int max_pages, int nq, int nkv,
     int page_size, float scale_log2, int window, int token_offset, const float* __restrict__ slopes,
-    const float* __restrict__ sinks) {
+    const float* __restrict__ sinks, int cache_nkv) {
     // token_offset: row of q and out at which the first of these requests begins (requests ahead of
     // them in the batch are another launch's); query_start holds rows of the whole batch.
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -425,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, EXACT ? 2 : 3) prefill_attention_ker
     const int seq_len = seq_lens[request];
     const int past = seq_len - q_len;
     const int head = blockIdx.y;
-    const int kv_head = head / (nq / nkv);
+    const int kv_head = (head / (nq / nkv)) / (nkv / cache_nkv);       // the cached head this query head reads
     const float slope = (EXACT && slopes != nullptr) ? slopes[head] * kLog2e : 0.0f;
     const int* table = block_table + (size_t)request * max_pages;
     const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
@@ -454,13 +457,13 @@ __global__ void __launch_bounds__(kThreads, EXACT ? 2 : 3) prefill_attention_ker
     auto k_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D; };
     auto v_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D + kKeys * D; };
 
-    load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, k_first, k_end, kv_head, nkv, page_size, page_shift);
+    load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, k_first, k_end, kv_head, cache_nkv, page_size, page_shift);
     cp_async_commit();
     for (int t = 0; t < tiles; ++t) {
         const int k0 = k_first + t * kKeys;
         if (t + 1 < tiles) {
             load_kv_tile<D>(k_stage((t + 1) & 1), v_stage((t + 1) & 1), k_pages, v_pages, table,
-                            k0 + kKeys, k_end, kv_head, nkv, page_size, page_shift);
+                            k0 + kKeys, k_end, kv_head, cache_nkv, page_size, page_shift);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -597,15 +600,17 @@ template <int D, bool EXACT = false>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o,
                   float* partial_ml, const int* seq_lens, const int* block_table, int num_requests,
                   int max_pages, int nq, int nkv, int page_size, float scale, int window, int splits,
-                  cudaStream_t stream, const float* slopes = nullptr, const float* sinks = nullptr) {
+                  cudaStream_t stream, const float* slopes = nullptr, const float* sinks = nullptr,
+                  int cache_nkv = 0) {
     auto kernel = decode_attention_kernel<D, EXACT>;
+    if (cache_nkv <= 0) cache_nkv = nkv;
     const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (status != cudaSuccess) return fail("decode_attention", cudaGetErrorString(status));
     dim3 grid(splits, nkv, num_requests);
     launch_overlapped(kernel, grid, kThreads, smem, stream,
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, partial_o, partial_ml,
-        seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits, slopes, sinks);
+        seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits, slopes, sinks, cache_nkv);
     if (int rc = check_launch("decode_attention")) return rc;
     if (splits > 1) {
         launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,
@@ -621,7 +626,8 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void
                    const int* query_start, const int* seq_lens, const int* block_table,
                    int num_requests, int num_tokens, int max_pages, int nq, int nkv, int page_size,
                    float scale, int window, int token_offset, cudaStream_t stream, const float* slopes = nullptr,
-                   const float* sinks = nullptr) {
+                   const float* sinks = nullptr, int cache_nkv = 0) {
+    if (cache_nkv <= 0) cache_nkv = nkv;
     auto kernel = prefill_attention_kernel<D, EXACT>;
     const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -630,7 +636,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void
     kernel<<<grid, kThreads, smem, stream>>>(
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, query_start, seq_lens,
         block_table, num_requests, max_pages, nq, nkv, page_size, scale * kLog2e, window, token_offset, slopes,
-        sinks);
+        sinks, cache_nkv);
     return check_launch("prefill_attention");
 }
 

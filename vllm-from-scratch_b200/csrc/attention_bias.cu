@@ -316,14 +316,19 @@ B200_EXPORT int b200_biased_attention_bf16_supports(int nq, int nkv, int d, int 
 
 B200_EXPORT int b200_biased_sm_count() { return b200::sm_count(); }
 
+// cache_nkv: the heads the pages hold; nkv may be a multiple of it, the query heads then form more groups
+// than there are cached heads and several groups read the same rows (many query heads on one cached head
+// run as groups of at most 16).
 // One query token per request (row r of q is request r).  With splits > 1, partial_o holds
 // [requests * nq * splits * d] floats and partial_ml [requests * nq * splits * 2] floats of scratch.
 B200_EXPORT int b200_biased_decode_attention_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o, float* partial_ml,
     const int* seq_lens, const int* block_table, const float* slopes, const float* sinks, int num_requests,
-    int max_pages, int nq, int nkv, int d, int page_size, float scale, int window, int splits, cudaStream_t stream) {
+    int max_pages, int nq, int nkv, int d, int page_size, float scale, int window, int splits, int cache_nkv,
+    cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0) return 0;
+    if (cache_nkv <= 0 || nkv % cache_nkv) return fail("biased_decode_attention", "the cached heads must divide the key/value heads");
     if (!b200_biased_attention_bf16_supports(nq, nkv, d, d)) return fail("biased_decode_attention", "shape not built");
     if (splits < 1 || nkv > 65535 || num_requests > 65535) return fail("biased_decode_attention", "grid out of range");
     if (splits > 1 && (partial_o == nullptr || partial_ml == nullptr))
@@ -332,7 +337,7 @@ B200_EXPORT int b200_biased_decode_attention_bf16(
     if (d == D)                                                                                              \
         return launch_decode<D, true>(q, k_pages, v_pages, out, partial_o, partial_ml, seq_lens, block_table, \
                                       num_requests, max_pages, nq, nkv, page_size, scale, window, splits,    \
-                                      stream, slopes, sinks);
+                                      stream, slopes, sinks, cache_nkv);
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("biased_decode_attention", "head_dim not built");
@@ -343,16 +348,18 @@ B200_EXPORT int b200_biased_decode_attention_bf16(
 B200_EXPORT int b200_biased_prefill_attention_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start, const int* seq_lens,
     const int* block_table, const float* slopes, const float* sinks, int num_requests, int num_tokens, int max_pages,
-    int nq, int nkv, int d, int page_size, float scale, int window, int token_offset, cudaStream_t stream) {
+    int nq, int nkv, int d, int page_size, float scale, int window, int token_offset, int cache_nkv,
+    cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0 || num_tokens - token_offset <= 0) return 0;
+    if (cache_nkv <= 0 || nkv % cache_nkv) return fail("biased_prefill_attention", "the cached heads must divide the key/value heads");
     if (token_offset < 0) return fail("biased_prefill_attention", "negative token offset");
     if (!b200_biased_attention_bf16_supports(nq, nkv, d, d)) return fail("biased_prefill_attention", "shape not built");
 #define B200_CASE(D)                                                                                           \
     if (d == D)                                                                                                \
         return launch_prefill<D, true>(q, k_pages, v_pages, out, query_start, seq_lens, block_table,           \
                                        num_requests, num_tokens, max_pages, nq, nkv, page_size, scale, window, \
-                                       token_offset, stream, slopes, sinks);
+                                       token_offset, stream, slopes, sinks, cache_nkv);
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("biased_prefill_attention", "head_dim not built");

@@ -173,9 +173,15 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
         _check("block table", block_table, torch.int32, (requests, None)),
         _check("slopes", slopes, torch.float32, (num_q_heads,), optional=True),
         _check("sinks", sinks, torch.float32, (num_q_heads,), optional=True))
+    # The decode kernel takes up to 16 query heads on a key/value head; more run as several groups that
+    # read the same cached head.
+    launch_kv = next(m for m in range(num_kv_heads, num_q_heads + 1, num_kv_heads)
+                     if num_q_heads % m == 0 and (num_q_heads // m <= 16 or m == num_q_heads))
     if (USE_TENSOR_CORES and dtype == torch.bfloat16 and max_query_len is not None and max_seq_len is not None
-            and head_dim == value_dim and head_dim in (64, 128, 256) and num_q_heads // num_kv_heads <= 16):
+            and head_dim == value_dim and head_dim in (64, 128, 256) and num_q_heads % launch_kv == 0
+            and num_q_heads // launch_kv <= 16):
         from .attention_bf16 import decode_splits
+        cached_heads, num_kv_heads = num_kv_heads, launch_kv
         q_p, k_p, v_p, out_p, start_p, lens_p, table_p, slopes_p, sinks_p = checked
         single = requests if (max_query_len == 1 and tokens == requests) else num_decode
         width = block_table.shape[1]
@@ -188,7 +194,7 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
             _run("attention_bias", "b200_biased_decode_attention_bf16", _P(q_p), _P(k_p), _P(v_p), _P(out_p),
                  _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
                  _P(lens_p), _P(table_p), _P(slopes_p), _P(sinks_p), _I(single), _I(width), _I(num_q_heads), _I(num_kv_heads),
-                 _I(head_dim), _I(page_size), _F(scale), _I(window or 0), _I(splits), _stream())
+                 _I(head_dim), _I(page_size), _F(scale), _I(window or 0), _I(splits), _I(cached_heads), _stream())
             if splits > 1:
                 count_launch()
         if single < requests:
@@ -198,7 +204,7 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                  _P(start_p + 4 * single), _P(lens_p + 4 * single), _P(table_p + 4 * single * width), _P(slopes_p),
                  _P(sinks_p),
                  _I(requests - single), _I(tokens), _I(width), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
-                 _I(page_size), _F(scale), _I(window or 0), _I(single), _stream())
+                 _I(page_size), _F(scale), _I(window or 0), _I(single), _I(cached_heads), _stream())
         return
     _run("attention_bias", "b200_biased_paged_attention",
          *(_P(address) for address in checked),
