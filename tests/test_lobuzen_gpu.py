@@ -461,3 +461,33 @@ def test_unit_norm_of_queries_and_keys_and_rows_of_keys_alone(dtype):
         if slot >= 0:
             assert torch.allclose(pages[slot // page, 0, slot % page].cpu().double(), want_c[t], atol=tol, rtol=tol)
     assert float(pages[0, 0, 2].abs().max()) == 0.0          # slot 2 was nobody's
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gathered_rows(dtype):
+    from vllm_from_scratch_b200.kernels import grouped
+    g = torch.Generator().manual_seed(12)
+    for width in (64, 50, 7):
+        x = torch.randn(20, width, generator=g).to(dtype)
+        index = torch.randint(0, 60, (33,), generator=g).int()
+        out = torch.empty(33, width, dtype=dtype, device="cuda")
+        grouped.gather_rows(dev(x), dev(index), 3, out)
+        assert torch.equal(out.cpu(), x[(index // 3).long()])
+
+
+def test_routed_experts_by_the_library_and_by_the_engine_agree(folders):
+    """Steps of many rows hand the experts' products to the library's grouped product, steps of few rows to
+    the engine's own kernel: the same rows up to rounding, for the same tokens."""
+    from vllm_from_scratch_b200.parts.feed_forward import RoutedExperts
+    raw, page_size = CONFIGS["B"]
+    sequences = {"x": helpers.random_tokens(raw["vocab"], 200, seed=5)}
+    results = []
+    for least in (1, 10 ** 9):
+        RoutedExperts.LIBRARY_MIN_ROWS, before = least, RoutedExperts.LIBRARY_MIN_ROWS
+        try:
+            runner = make_runner(folders["B", "bfloat16"], "bfloat16", page_size, 14)
+            results.append(helpers.run_schedule(runner, sequences, [[("x", 200)]])["x"])
+        finally:
+            RoutedExperts.LIBRARY_MIN_ROWS = before
+    scale = float(results[0].abs().max())
+    assert float((results[0] - results[1]).abs().max()) <= 0.03 * scale

@@ -26,6 +26,14 @@ using bf16 = __nv_bfloat16;
 
 __device__ __forceinline__ float sigmoid_fn(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+__device__ __forceinline__ float4 load_four(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load_four(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__bfloat162float(lo.x), __bfloat162float(lo.y), __bfloat162float(hi.x), __bfloat162float(hi.y));
+}
+
 // ------------------------------------------------------------------------------- routing
 // (value, index) pairs in the order "larger value first, then smaller index": true if a comes before b.
 __device__ __forceinline__ bool ahead(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
@@ -44,10 +52,25 @@ __global__ void route_experts_kernel(const T* __restrict__ x, const float* __res
     const int token = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const T* row = x + (size_t)token * K;
+    // Four consecutive elements a lane and step where the rows allow it (every lane's partial sums and the
+    // order in which they are added depend on K alone, so a token's logits do not depend on the batch).
+    const bool vector_ok = (K % 4 == 0) && (((uintptr_t)router | (uintptr_t)x) & 15) == 0 && ((K * sizeof(T)) % 8 == 0);
     for (int e = warp; e < E; e += warps) {
         const float* w = router + (size_t)e * K;
         float sum = 0.0f;
-        for (int k = lane; k < K; k += 32) sum = fmaf(w[k], to_float(row[k]), sum);
+        if (vector_ok) {
+            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int k = lane * 4; k < K; k += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + k);
+                const float4 xv = load_four(row + k);
+                part[0] = fmaf(wv.x, xv.x, part[0]); part[1] = fmaf(wv.y, xv.y, part[1]);
+                part[2] = fmaf(wv.z, xv.z, part[2]); part[3] = fmaf(wv.w, xv.w, part[3]);
+            }
+            sum = (part[0] + part[1]) + (part[2] + part[3]);
+        } else {
+            for (int k = lane; k < K; k += 32) sum = fmaf(w[k], to_float(row[k]), sum);
+        }
         sum = warp_sum(sum);
         if (lane == 0) {
             const float s = sigmoid_fn(sum);
@@ -167,6 +190,23 @@ __global__ void combine_experts_kernel(const T* __restrict__ rows, const int* __
     }
 }
 
+// out[r] = x[index[r] / divisor]: the tokens' rows in the order of the experts' lists, for a product that
+// wants every list's rows side by side.
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ index, int divisor,
+                                   T* __restrict__ out, int width) {
+    const size_t row = blockIdx.x;
+    const T* src = x + (size_t)(index[row] / divisor) * width;
+    T* dst = out + row * width;
+    const int per = 16 / (int)sizeof(T);
+    if (width % per == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        for (int i = threadIdx.x; i < width / per; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
 // ----------------------------------------------------------------------- grouped products
 struct GroupedArgs {
     const void* a;          // rows of A
@@ -242,7 +282,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(kThreadsG) grouped_gemm_bf16_kernel(const GroupedArgs p) {
     overlap_trigger();
     overlap_wait();
-    constexpr int BK = 32, LD = BK + 8;
+    constexpr int BK = 64, LD = BK + 8;
     constexpr int NB = GATED ? 2 : 1;
     __shared__ __align__(16) bf16 a_s[kBM][LD];
     __shared__ __align__(16) bf16 b_s[NB][kBN][LD];
@@ -257,8 +297,8 @@ __global__ void __launch_bounds__(kThreadsG) grouped_gemm_bf16_kernel(const Grou
     const bool vector_ok = (K % 8 == 0) && (p.lda % 8 == 0) && (p.a_group % 8 == 0)
                            && (((uintptr_t)p.a | (uintptr_t)p.w) & 15) == 0;
 
-    // This thread's share of a tile: one piece of eight of A, two of each B.
-    const int a_r = tid >> 2, a_k = (tid & 3) * 8;
+    // This thread's share of a tile: two pieces of eight of a row of A, and of two rows of each B.
+    const int a_r = tid >> 2, a_k = (tid & 3) * 16;
     const bf16* a_src = a_r < rows_here ? a + a_row_of(p, list_base + row0 + a_r) * p.lda : nullptr;
     const bf16* b_src[NB][2];
 #pragma unroll
@@ -274,29 +314,33 @@ __global__ void __launch_bounds__(kThreadsG) grouped_gemm_bf16_kernel(const Grou
 #pragma unroll
         for (int t = 0; t < 4; ++t) acc[h][t][0] = acc[h][t][1] = acc[h][t][2] = acc[h][t][3] = 0.0f;
 
-    uint4 a_next = load8(a_src, a_k, K, vector_ok);
-    uint4 b_next[NB][2];
+    uint4 a_next[2], b_next[NB][2][2];
+    auto fetch = [&](int k) {
 #pragma unroll
-    for (int h = 0; h < NB; ++h)
+        for (int piece = 0; piece < 2; ++piece) {
+            a_next[piece] = load8(a_src, k + a_k + 8 * piece, K, vector_ok);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) b_next[h][i] = load8(b_src[h][i], a_k, K, vector_ok);
+            for (int h = 0; h < NB; ++h)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) b_next[h][i][piece] = load8(b_src[h][i], k + a_k + 8 * piece, K, vector_ok);
+        }
+    };
+    fetch(0);
 
     const int g = lane >> 2, t4 = lane & 3;
     for (int k0 = 0; k0 < K; k0 += BK) {
         __syncthreads();
-        *reinterpret_cast<uint4*>(&a_s[a_r][a_k]) = a_next;
 #pragma unroll
-        for (int h = 0; h < NB; ++h)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) *reinterpret_cast<uint4*>(&b_s[h][(tid >> 2) + 32 * i][a_k]) = b_next[h][i];
-        __syncthreads();
-        if (k0 + BK < K) {
-            a_next = load8(a_src, k0 + BK + a_k, K, vector_ok);
+        for (int piece = 0; piece < 2; ++piece) {
+            *reinterpret_cast<uint4*>(&a_s[a_r][a_k + 8 * piece]) = a_next[piece];
 #pragma unroll
             for (int h = 0; h < NB; ++h)
 #pragma unroll
-                for (int i = 0; i < 2; ++i) b_next[h][i] = load8(b_src[h][i], k0 + BK + a_k, K, vector_ok);
+                for (int i = 0; i < 2; ++i)
+                    *reinterpret_cast<uint4*>(&b_s[h][(tid >> 2) + 32 * i][a_k + 8 * piece]) = b_next[h][i][piece];
         }
+        __syncthreads();
+        if (k0 + BK < K) fetch(k0 + BK);
 #pragma unroll
         for (int kk = 0; kk < BK; kk += 16) {
             unsigned af[4];
@@ -481,6 +525,21 @@ B200_EXPORT int b200_expert_lists(const int* ids, int pairs, int E, int* offsets
     launch_overlapped_if(pairs <= 8 * kOverlapMostRows, expert_lists_kernel, 1, pairs > 256 ? 1024 : 256,
                          (size_t)E * sizeof(int), stream, ids, pairs, E, offsets, sorted_pair, position);
     return check_launch("expert_lists");
+}
+
+B200_EXPORT int b200_gather_rows(const void* x, const int* index, int divisor, void* out, int rows, int width,
+                                 int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (rows == 0) return 0;
+    if (divisor <= 0 || width <= 0) return fail("gather_rows", "sizes out of range");
+    if (dtype == 0)
+        gather_rows_kernel<float><<<rows, 128, 0, stream>>>((const float*)x, index, divisor, (float*)out, width);
+    else if (dtype == 1)
+        gather_rows_kernel<__nv_bfloat16><<<rows, 128, 0, stream>>>((const __nv_bfloat16*)x, index, divisor,
+                                                                  (__nv_bfloat16*)out, width);
+    else
+        return fail("gather_rows", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("gather_rows");
 }
 
 B200_EXPORT int b200_combine_experts(const void* rows, const int* position, const float* weights, void* out,

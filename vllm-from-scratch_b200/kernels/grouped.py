@@ -50,6 +50,14 @@ def expert_lists(ids: torch.Tensor, experts: int, offsets: torch.Tensor, sorted_
          _P(_check("rows of the pairs", position, torch.int32, (pairs,))), _stream())
 
 
+def gather_rows(x: torch.Tensor, index: torch.Tensor, divisor: int, out: torch.Tensor) -> None:
+    """``out[r] = x[index[r] // divisor]``."""
+    rows, width = out.shape
+    _run("grouped", "b200_gather_rows", _P(_check("rows to gather from", x, _RUN, (None, width))),
+         _P(_check("row index", index, torch.int32, (rows,))), _I(divisor), _P(_check("gathered rows", out, x.dtype)),
+         _I(rows), _I(width), _I(_code(x.dtype)), _stream())
+
+
 def combine_experts(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
     """``out[t] = sum_j weights[t, j] * rows[position[t * top + j]]`` in float32, j in order."""
     tokens, width = out.shape

@@ -169,6 +169,13 @@ class RoutedExperts(FeedForward):
         self.gate_up = torch.stack([torch.cat([tensors[gate], tensors[up]], dim=0) for gate, up, _ in names]).contiguous()
         self.down = torch.stack([tensors[down] for _, _, down in names]).contiguous()
 
+    # From this many rows over all lists on, bfloat16 products whose sizes the library takes go to it.
+    LIBRARY_MIN_ROWS = 256
+
+    def _library_takes(self, x: torch.Tensor, rows: int) -> bool:
+        return (x.dtype == torch.bfloat16 and rows >= self.LIBRARY_MIN_ROWS and hasattr(torch, "_grouped_mm")
+                and x.shape[1] % 8 == 0 and self.intermediate_size % 8 == 0)
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         from ..kernels import grouped
         tokens, device = x.shape[0], x.device
@@ -177,13 +184,25 @@ class RoutedExperts(FeedForward):
         weights = torch.empty((tokens, top), dtype=torch.float32, device=device)
         grouped.route_experts(x, self.router, self.correction, ids, weights, top, self.group_count,
                               self.group_keep, self.group_top)
-        books = torch.empty(experts + 1 + 2 * tokens * top, dtype=torch.int32, device=device)
-        offsets, sorted_pair, position = torch.split(books, [experts + 1, tokens * top, tokens * top])
+        # three words ahead of the offsets, so that offsets[1:] (where each list ends) begins at 16 bytes
+        books = torch.empty(3 + experts + 1 + 2 * tokens * top, dtype=torch.int32, device=device)
+        _, offsets, sorted_pair, position = torch.split(books, [3, experts + 1, tokens * top, tokens * top])
         grouped.expert_lists(ids, experts, offsets, sorted_pair, position)
         hidden = torch.empty((tokens * top, self.intermediate_size), dtype=x.dtype, device=device)
-        grouped.expert_gemm(x, self.gate_up, hidden, offsets, sorted_pair, top, gated="silu")
-        rows = torch.empty((tokens * top, self.env.hidden_size), dtype=x.dtype, device=device)
-        grouped.expert_gemm(hidden, self.down, rows, offsets, None)
+        if self._library_takes(x, tokens * top):
+            # Many rows: the library's grouped product over the rows put side by side list by list (as the
+            # engine's large plain products go to the library), the activation as a kernel of its own.
+            gathered = torch.empty((tokens * top, x.shape[1]), dtype=x.dtype, device=device)
+            grouped.gather_rows(x, sorted_pair, top, gathered)
+            gate_up = torch._grouped_mm(gathered, self.gate_up.transpose(1, 2), offs=offsets[1:])
+            kernels.count_launch()
+            kernels.silu_mul(gate_up, hidden)
+            rows = torch._grouped_mm(hidden, self.down.transpose(1, 2), offs=offsets[1:])
+            kernels.count_launch()
+        else:
+            rows = torch.empty((tokens * top, self.env.hidden_size), dtype=x.dtype, device=device)
+            grouped.expert_gemm(x, self.gate_up, hidden, offsets, sorted_pair, top, gated="silu")
+            grouped.expert_gemm(hidden, self.down, rows, offsets, None)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=device)
         grouped.combine_experts(rows, position, weights, out)
         return out
