@@ -60,7 +60,7 @@ __global__ void route_experts_kernel(const T* __restrict__ x, const float* __res
         float sum = 0.0f;
         if (vector_ok) {
             float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
+#pragma unroll 8
             for (int k = lane * 4; k < K; k += 128) {
                 const float4 wv = *reinterpret_cast<const float4*>(w + k);
                 const float4 xv = load_four(row + k);
@@ -506,11 +506,13 @@ B200_EXPORT int b200_route_experts(const void* x, const float* router, const flo
         return fail("route_experts", "the kept groups hold fewer experts than are to be chosen");
     const size_t smem = sizeof(float) * (2 * (size_t)E + group_count);
     if (smem > 48 * 1024) return fail("route_experts", "too many experts for one block's shared memory");
+    // a warp an expert where few tokens leave the SMs room for it
+    const int threads = (tokens <= 4 * kOverlapMostRows && E > 4) ? 256 : 128;
     if (dtype == 0)
-        launch_overlapped_if(tokens <= kOverlapMostRows, route_experts_kernel<float>, tokens, 128, smem, stream,
+        launch_overlapped_if(tokens <= kOverlapMostRows, route_experts_kernel<float>, tokens, threads, smem, stream,
             (const float*)x, router, correction, ids, weights, K, E, top, group_count, group_keep, group_top);
     else if (dtype == 1)
-        launch_overlapped_if(tokens <= kOverlapMostRows, route_experts_kernel<__nv_bfloat16>, tokens, 128, smem, stream,
+        launch_overlapped_if(tokens <= kOverlapMostRows, route_experts_kernel<__nv_bfloat16>, tokens, threads, smem, stream,
             (const __nv_bfloat16*)x, router, correction, ids, weights, K, E, top, group_count, group_keep, group_top);
     else
         return fail("route_experts", "dtype must be 0 (float32) or 1 (bfloat16)");
