@@ -280,14 +280,15 @@ def test_routing(router, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(50, 33, 5, 2), (64, 40, 8, 3), (128, 96, 3, 1), (37, 9, 4, 4)])
-def test_expert_products(dtype, sizes):
+@pytest.mark.parametrize("tokens", [75, 9])
+@pytest.mark.parametrize("sizes", [(50, 33, 5, 2), (64, 40, 8, 3), (128, 96, 3, 1), (37, 9, 4, 4), (256, 64, 6, 2)])
+def test_expert_products(dtype, sizes, tokens):
     """Lists per expert, the two grouped products and the weighted sum against a loop over tokens; some
-    experts get no token, some get more than a tile of rows."""
+    experts get no token, some get more than a tile of rows.  Few tokens with widths that are multiples of
+    32 run in the kernel of many small blocks, everything else in tiles of 32 rows."""
     from vllm_from_scratch_b200.kernels import grouped
     width, inter, experts, top = sizes
     g = torch.Generator().manual_seed(7)
-    tokens = 75
     x = torch.randn(tokens, width, generator=g).to(dtype)
     gate_up = (torch.randn(experts, 2 * inter, width, generator=g) / width ** 0.5).to(dtype)
     down = (torch.randn(experts, width, inter, generator=g) / inter ** 0.5).to(dtype)
@@ -329,13 +330,13 @@ def test_expert_products(dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(4, 16, 32, 0), (3, 6, 22, 10), (8, 32, 128, 64), (1, 20, 18, 3)])
-def test_products_per_head(dtype, sizes):
+@pytest.mark.parametrize("tokens", [45, 130])
+@pytest.mark.parametrize("sizes", [(4, 16, 32, 0), (3, 6, 22, 10), (8, 32, 128, 64), (1, 20, 18, 3), (5, 128, 24, 8)])
+def test_products_per_head(dtype, sizes, tokens):
     """A matrix per head over rows that hold the heads side by side, beginning at a column of a wider row."""
     from vllm_from_scratch_b200.kernels import grouped
     heads, k, n, column = sizes
     g = torch.Generator().manual_seed(8)
-    tokens = 45
     x = torch.randn(tokens, column + heads * k + 5, generator=g).to(dtype)
     w = (torch.randn(heads, n, k, generator=g) / k ** 0.5).to(dtype)
     out = torch.empty(tokens, heads * n, dtype=dtype, device="cuda")

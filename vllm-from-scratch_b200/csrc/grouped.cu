@@ -34,6 +34,15 @@ __device__ __forceinline__ float4 load_four(const bf16* p) {
     return make_float4(__bfloat162float(lo.x), __bfloat162float(lo.y), __bfloat162float(hi.x), __bfloat162float(hi.y));
 }
 
+__device__ __forceinline__ void store_four(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store_four(bf16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned*>(&lo);
+    raw.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // ------------------------------------------------------------------------------- routing
 // (value, index) pairs in the order "larger value first, then smaller index": true if a comes before b.
 __device__ __forceinline__ bool ahead(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
@@ -180,6 +189,22 @@ __global__ void combine_experts_kernel(const T* __restrict__ rows, const int* __
     overlap_trigger();
     overlap_wait();
     const int token = blockIdx.x;
+    if (width % 4 == 0 && (((uintptr_t)rows | (uintptr_t)out) & 15) == 0) {
+        // four columns a thread and step: the same sums in the same order, fewer and wider loads
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int j = 0; j < top; ++j) {
+                const int row = position[(size_t)token * top + j];
+                if (row < 0) continue;
+                const float w = weights[(size_t)token * top + j];
+                const float4 v = load_four(rows + (size_t)row * width + i);
+                sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y);
+                sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
+            }
+            store_four(out + (size_t)token * width + i, sum);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float sum = 0.0f;
         for (int j = 0; j < top; ++j) {
@@ -235,26 +260,27 @@ constexpr int kBM = 32, kBN = 64, kThreadsG = 128;
 
 // Which group and which tile of its rows a block has: group g owns blocks [first(g), first(g + 1)) with
 // first(g) = offsets[g] / kBM + g, which leaves every group ceil(rows / kBM) blocks at least.
+template <int BM = kBM>
 __device__ __forceinline__ bool find_tile(const GroupedArgs& p, int block, int& group, int& row0, int& rows_here,
                                           int& list_base) {
     if (p.offsets == nullptr) {
-        const int tiles = (p.rows + kBM - 1) / kBM;
+        const int tiles = (p.rows + BM - 1) / BM;
         group = block / tiles;
-        row0 = (block - group * tiles) * kBM;
+        row0 = (block - group * tiles) * BM;
         list_base = 0;
-        rows_here = min(kBM, p.rows - row0);
+        rows_here = min(BM, p.rows - row0);
         return group < p.groups && rows_here > 0;
     }
     int lo = 0, hi = p.groups - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
-        if (p.offsets[mid] / kBM + mid <= block) lo = mid; else hi = mid - 1;
+        if (p.offsets[mid] / BM + mid <= block) lo = mid; else hi = mid - 1;
     }
     group = lo;
     list_base = p.offsets[group];
     const int count = p.offsets[group + 1] - list_base;
-    row0 = (block - (list_base / kBM + group)) * kBM;
-    rows_here = min(kBM, count - row0);
+    row0 = (block - (list_base / BM + group)) * BM;
+    rows_here = min(BM, count - row0);
     return rows_here > 0;
 }
 
@@ -384,6 +410,100 @@ __global__ void __launch_bounds__(kThreadsG) grouped_gemm_bf16_kernel(const Grou
     }
 }
 
+// Few rows over all lists (a decode step): the time is the stream of the matrices, so a block takes 16 rows
+// of a list against only 16 columns (gated: 16 gate and 16 up rows of the matrix) over all of K, its four
+// warps a quarter of the k-steps each, and every lane asks for its fragments of four k-steps (up to 24 loads
+// of 16 bytes) before it multiplies: many small blocks with much in flight.  Fragments come straight from
+// global memory: a lane's 16 bytes of a row are the operands of two m16n8k16 products, with the sixteen k of
+// a product taken in the order in which the lanes hold them, the same for both operands.  The warps' sums
+// meet in shared memory and are added in the order of the warps.  K a multiple of 32, rows 16-byte aligned.
+constexpr int kFM = 16, kFN = 16;
+constexpr int kFewRowsMost = 64;        // rows (of all lists; of a group without lists) up to which it is used
+
+template <bool GATED>
+__global__ void __launch_bounds__(kThreadsG) grouped_few_rows_bf16_kernel(const GroupedArgs p) {
+    overlap_trigger();
+    overlap_wait();
+    constexpr int NB = GATED ? 2 : 1, NT = kFN / 8, U = 4;
+    __shared__ float red[4][NB][kFM][kFN + 1];
+    int group, row0, rows_here, list_base;
+    if (!find_tile<kFM>(p, blockIdx.x, group, row0, rows_here, list_base)) return;
+    const int n0 = blockIdx.y * kFN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int K = p.K, N = p.N;
+    const bf16* a = (const bf16*)p.a + (long long)group * p.a_group;
+    const bf16* w = (const bf16*)p.w + (long long)group * (long long)(NB * N) * K;
+    const bf16* a_lo = g < rows_here ? a + a_row_of(p, list_base + row0 + g) * p.lda : nullptr;
+    const bf16* a_hi = g + 8 < rows_here ? a + a_row_of(p, list_base + row0 + g + 8) * p.lda : nullptr;
+    const bf16* b_row[NB][NT];
+#pragma unroll
+    for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int n = n0 + nt * 8 + g;
+            b_row[h][nt] = n < N ? w + ((long long)h * N + n) * K : nullptr;
+        }
+    float acc[NB][NT][4];
+#pragma unroll
+    for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) acc[h][nt][0] = acc[h][nt][1] = acc[h][nt][2] = acc[h][nt][3] = 0.0f;
+
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const int steps = K / 32;
+    for (int s0 = warp; s0 < steps; s0 += 4 * U) {
+        uint4 av[U][2], bv[U][NB][NT];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + 4 * u;
+            const int k = s * 32 + t4 * 8;
+            const bool in = s < steps;
+            av[u][0] = in && a_lo ? *reinterpret_cast<const uint4*>(a_lo + k) : zero;
+            av[u][1] = in && a_hi ? *reinterpret_cast<const uint4*>(a_hi + k) : zero;
+#pragma unroll
+            for (int h = 0; h < NB; ++h)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                    bv[u][h][nt] = in && b_row[h][nt] ? *reinterpret_cast<const uint4*>(b_row[h][nt] + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const unsigned first[4] = {av[u][0].x, av[u][1].x, av[u][0].y, av[u][1].y};
+            const unsigned second[4] = {av[u][0].z, av[u][1].z, av[u][0].w, av[u][1].w};
+#pragma unroll
+            for (int h = 0; h < NB; ++h)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_bf16(acc[h][nt], first, bv[u][h][nt].x, bv[u][h][nt].y);
+                    mma_bf16(acc[h][nt], second, bv[u][h][nt].z, bv[u][h][nt].w);
+                }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            red[warp][h][g][nt * 8 + 2 * t4] = acc[h][nt][0];
+            red[warp][h][g][nt * 8 + 2 * t4 + 1] = acc[h][nt][1];
+            red[warp][h][g + 8][nt * 8 + 2 * t4] = acc[h][nt][2];
+            red[warp][h][g + 8][nt * 8 + 2 * t4 + 1] = acc[h][nt][3];
+        }
+    __syncthreads();
+    bf16* c = (bf16*)p.c + (long long)group * p.c_group;
+    for (int idx = tid; idx < kFM * kFN; idx += kThreadsG) {
+        const int r = idx / kFN, col = idx - r * kFN;
+        if (r >= rows_here || n0 + col >= N) continue;
+        float v[NB];
+#pragma unroll
+        for (int h = 0; h < NB; ++h) v[h] = ((red[0][h][r][col] + red[1][h][r][col]) + red[2][h][r][col]) + red[3][h][r][col];
+        float value = v[0];
+        if (GATED)
+            value = gated_value(__bfloat162float(__float2bfloat16_rn(v[0])), __bfloat162float(__float2bfloat16_rn(v[NB - 1])), p);
+        c[(long long)(list_base + row0 + r) * p.ldc + n0 + col] = __float2bfloat16_rn(value);
+    }
+}
+
 template <bool GATED>
 __global__ void __launch_bounds__(kThreadsG) grouped_gemm_f32_kernel(const GroupedArgs p) {
     overlap_trigger();
@@ -461,6 +581,19 @@ __global__ void capped_swish_mul_kernel(const T* __restrict__ gate_up, T* __rest
     overlap_wait();
     const size_t token = blockIdx.x;
     const T* row = gate_up + token * 2 * (size_t)inter;
+    if (inter % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < inter; i += gridDim.y * blockDim.x * 4) {
+            const float4 gv = load_four(row + i), uv = load_four(row + inter + i);
+            float4 r;
+            float g, u;
+            g = fminf(gv.x, limit); u = fminf(fmaxf(uv.x, -limit), limit); r.x = g * sigmoid_fn(slope * g) * (u + offset);
+            g = fminf(gv.y, limit); u = fminf(fmaxf(uv.y, -limit), limit); r.y = g * sigmoid_fn(slope * g) * (u + offset);
+            g = fminf(gv.z, limit); u = fminf(fmaxf(uv.z, -limit), limit); r.z = g * sigmoid_fn(slope * g) * (u + offset);
+            g = fminf(gv.w, limit); u = fminf(fmaxf(uv.w, -limit), limit); r.w = g * sigmoid_fn(slope * g) * (u + offset);
+            store_four(out + token * inter + i, r);
+        }
+        return;
+    }
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
         const float g = fminf(to_float(row[i]), limit);
         const float u = fminf(fmaxf(to_float(row[inter + i]), -limit), limit);
@@ -586,7 +719,18 @@ B200_EXPORT int b200_grouped_gemm(const void* a, const void* w, void* c, const i
     p.c_group = c_group; p.act_limit = limit; p.act_slope = slope; p.act_offset = offset;
     p.act_kind = gated == 2 ? 1 : 0;
     const dim3 grid((unsigned)tiles, n_tiles);
+    const int all_rows = offsets ? list_rows : rows * groups;
     const bool overlap = (offsets ? list_rows : rows) <= kOverlapMostRows;
+    // Few rows in all: the stream of the matrices sets the time, and the kernel of many small blocks serves.
+    if (dtype == 1 && all_rows <= kFewRowsMost * (offsets ? 1 : groups) && K % 32 == 0 && lda % 8 == 0 && a_group % 8 == 0
+        && (((uintptr_t)a | (uintptr_t)w) & 15) == 0) {
+        const long long few_tiles = offsets ? (long long)list_rows / kFM + groups : (long long)groups * ((rows + kFM - 1) / kFM);
+        const dim3 few_grid((unsigned)few_tiles, (N + kFN - 1) / kFN);
+        if (few_grid.y > 65535) return fail("grouped_gemm", "grid out of range");
+        if (gated) launch_overlapped_if(overlap, grouped_few_rows_bf16_kernel<true>, few_grid, kThreadsG, 0, stream, p);
+        else launch_overlapped_if(overlap, grouped_few_rows_bf16_kernel<false>, few_grid, kThreadsG, 0, stream, p);
+        return check_launch("grouped_gemm");
+    }
     if (dtype == 0) {
         if (gated) launch_overlapped_if(overlap, grouped_gemm_f32_kernel<true>, grid, kThreadsG, 0, stream, p);
         else launch_overlapped_if(overlap, grouped_gemm_f32_kernel<false>, grid, kThreadsG, 0, stream, p);
@@ -603,7 +747,7 @@ B200_EXPORT int b200_capped_swish_mul(const void* gate_up, void* out, int tokens
                                       float slope, float offset, int dtype, cudaStream_t stream) {
     using namespace b200;
     if (tokens == 0 || inter == 0) return 0;
-    const dim3 grid(tokens, min(8, (inter + 1023) / 1024));
+    const dim3 grid(tokens, tokens >= 512 ? 1 : min(8, (inter + 1023) / 1024));
     if (dtype == 0)
         launch_overlapped_if(tokens <= kOverlapMostRows, capped_swish_mul_kernel<float>, grid, 256, 0, stream,
             (const float*)gate_up, (float*)out, inter, limit, slope, offset);
