@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(kThreadsG) grouped_gemm_bf16_kernel(const Grou
 // a product taken in the order in which the lanes hold them, the same for both operands.  The warps' sums
 // meet in shared memory and are added in the order of the warps.  K a multiple of 32, rows 16-byte aligned.
 constexpr int kFM = 16, kFN = 16;
-constexpr int kFewRowsMost = 64;        // rows (of all lists; of a group without lists) up to which it is used
+constexpr int kFewRowsMost = 64;  // rows (of all lists; of a group without lists) up to which it is used
 
 template <bool GATED>
 __global__ void __launch_bounds__(kThreadsG) grouped_few_rows_bf16_kernel(const GroupedArgs p) {
