@@ -11,6 +11,10 @@
 //                      rows gathered from the tokens, written one after another).  bfloat16: mma.sync
 //                      m16n8k16 with float32 accumulation; float32: fused multiply-adds in the order
 //                      of k.  GATED: W_g holds 2 N rows, gate rows first, and C = act(gate) * up.
+//                      Two forms in bfloat16: tiles of 32 x 64 staged through shared memory, and, for the
+//                      few rows of a decode step, many small blocks that stream the matrices (see
+//                      grouped_few_rows_bf16_kernel)
+//   gather_rows        the tokens' rows list by list, for a library product that wants them side by side
 //   combine_experts    y_t = sum over a token's choices of weight * its row, in float32, in the
 //                      order of the choices
 //   capped_swish_mul   out = g * sigmoid(slope g) * (u + offset), g = min(gate, limit), u = clamp(up)
