@@ -77,10 +77,25 @@ LZ_D = {
     ],
 }
 
-CONFIGS = {"A": (LZ_A, 16), "B": (LZ_B, 16), "C": (LZ_C, 4), "D": (LZ_D, 32)}
+# Wider: products over a width that the kernels for few rows take whole, sixteen experts in four groups,
+# 32 heads on one cached head (two groups of 16 on the tensor-core kernels), latent rows of a size that only
+# the float32-arithmetic kernel takes, a reader of them.
+LZ_E = {
+    "architecture": "Lobuzen", "vocab": 500, "width": 384, "norm": {"eps": 1e-5}, "token_side": {"dim": 16},
+    "layers": [
+        _attention(6, 3, 64, 64, 0.125, 50, _dense(448, 2.5)),
+        _latent(6, 32, 64, 96, 0.2, 100, _moe(160, 16, 4, 4, 2)),
+        _attention(12, 1, 32, 48, 0.18, 30, _moe(96, 16, 6, 2, 1)),
+        _latent(3, 64, 32, 96, 0.12, 60, _moe(160, 16, 4, 4, 2), kv_from=1),
+        _latent(32, 16, 16, 64, 0.25, 80, _dense(320, 1.0)),
+    ],
+}
+
+CONFIGS = {"A": (LZ_A, 16), "B": (LZ_B, 16), "C": (LZ_C, 4), "D": (LZ_D, 32), "E": (LZ_E, 16)}
 LENGTHS = {
     "A": {"a": 70, "b": 45, "c": 100, "d": 37, "e": 64, "f": 1, "g": 150},
     "B": {"a": 70, "b": 33, "c": 130, "d": 2, "e": 64, "g": 200},
     "C": {"a": 41, "b": 2, "c": 23, "g": 70},
     "D": {"a": 70, "b": 1, "c": 140, "g": 230},
+    "E": {"a": 300, "b": 64, "c": 129, "g": 260},
 }

@@ -387,7 +387,8 @@ def test_attention_over_shared_rows_with_sinks_and_windows(dtype, shape):
     for at, key in {300: 300 - window + 1, 301: 301 - window, 302: 288, 303: 287, 304: 304, 332: inside, 331: outside - 1}.items():
         if 0 <= key <= at:
             point(sequences[2], at, key)
-    point(sequences[0], 1499, 1499 - window)         # just outside
+    point(sequences[0], 1499, 1499 - window)         # just outside, for a token decoded alone
+    point(sequences[1], 49, max(0, 49 - window + 1))   # the oldest row inside, for a token decoded alone
     tokens = sum(fresh)
     q_rows = torch.zeros(tokens, H * d, dtype=torch.float64)
     want = torch.zeros(tokens, H * d, dtype=torch.float64)
