@@ -493,3 +493,42 @@ def test_routed_experts_by_the_library_and_by_the_engine_agree(folders):
             RoutedExperts.LIBRARY_MIN_ROWS = before
     scale = float(results[0].abs().max())
     assert float((results[0] - results[1]).abs().max()) <= 0.03 * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_program(folders, references, tmp_path, dtype):
+    """``bin/trace_run`` in a process of its own: a mixed schedule of up to four live requests over a pool
+    of 4 x 128 positions, logits of every place written step by step."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+    root = Path(__file__).resolve().parent.parent
+    name = "A"
+    raw, page_size = CONFIGS[name]
+    sequences, expected = references[name, dtype]
+    lengths = {rid: min(n, 128) for rid, n in LENGTHS[name].items()}
+    sequences = {rid: tokens[:lengths[rid]] for rid, tokens in sequences.items()}
+    steps = helpers.cut_mixed(lengths, seed=5, live=4)
+    lines = helpers.schedule_to_trace(sequences, steps)
+    out = tmp_path / "out"
+    process = subprocess.run(
+        [sys.executable, str(root / "bin" / "trace_run"), "--model", str(folders[name, dtype]), "--dtype", dtype,
+         "--out", str(out), "--max-tokens", str(4 * 128)],
+        input="\n".join(json.dumps(line) for line in lines) + "\n", capture_output=True, text=True,
+        timeout=900, env={**os.environ, "PYTHONPATH": ""})
+    assert process.returncode == 0, process.stderr[-3000:]
+    assert [l for l in process.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(len(lines))]
+    results: dict = {rid: [] for rid in sequences}
+    for line in lines:
+        data = torch.from_numpy(np.fromfile(out / f"{line['step']}.f32", dtype="<f4").reshape(-1, raw["vocab"]).copy())
+        at = 0
+        for entry in line["entries"]:
+            results[entry["id"]].append(data[at:at + len(entry["tokens"])])
+            at += len(entry["tokens"])
+        assert at == data.shape[0]
+    compare({rid: torch.cat(rows) for rid, rows in results.items()},
+            {rid: expected[rid][:lengths[rid]] for rid in sequences}, dtype, f"replay program/{dtype}")
