@@ -422,10 +422,19 @@ __global__ void __launch_bounds__(kThreadsG) grouped_gemm_bf16_kernel(const Grou
 // a product taken in the order in which the lanes hold them, the same for both operands.  The warps' sums
 // meet in shared memory and are added in the order of the warps.  K a multiple of 32, rows 16-byte aligned.
 constexpr int kFM = 16, kFN = 16;
-constexpr int kFewRowsMost = 64;  // rows (of all lists; of a group without lists) up to which it is used
+
+// 16 bytes that are read once.  `volatile` keeps the loads of a lane in the order written, ahead of the
+// products (which are `volatile` too): the compiler would otherwise hold back some of them to save registers.
+__device__ __forceinline__ uint4 load_stream16(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+constexpr int kFewRowsMost = 128; // rows (of all lists; of a group without lists) up to which it is used
 
 template <bool GATED>
-__global__ void __launch_bounds__(kThreadsG) grouped_few_rows_bf16_kernel(const GroupedArgs p) {
+__global__ void __launch_bounds__(kThreadsG, 3) grouped_few_rows_bf16_kernel(const GroupedArgs p) {
     overlap_trigger();
     overlap_wait();
     constexpr int NB = GATED ? 2 : 1, NT = kFN / 8, U = 4;
@@ -438,16 +447,22 @@ __global__ void __launch_bounds__(kThreadsG) grouped_few_rows_bf16_kernel(const 
     const int K = p.K, N = p.N;
     const bf16* a = (const bf16*)p.a + (long long)group * p.a_group;
     const bf16* w = (const bf16*)p.w + (long long)group * (long long)(NB * N) * K;
-    const bf16* a_lo = g < rows_here ? a + a_row_of(p, list_base + row0 + g) * p.lda : nullptr;
-    const bf16* a_hi = g + 8 < rows_here ? a + a_row_of(p, list_base + row0 + g + 8) * p.lda : nullptr;
+    // A row that does not exist is read from one that does (the tile's first, the matrix's first): every
+    // lane then issues the same loads, all of them before the first product.  What such a row gives lands
+    // in a row or a column of the result that is not stored (a row of the result depends on its own row of
+    // A alone, a column on its own row of W).
+    const bool has_lo = g < rows_here, has_hi = g + 8 < rows_here;
+    const bf16* a_lo = a + a_row_of(p, list_base + row0 + (has_lo ? g : 0)) * p.lda;
+    const bf16* a_hi = a + a_row_of(p, list_base + row0 + (has_hi ? g + 8 : 0)) * p.lda;
     const bf16* b_row[NB][NT];
+    bool has_b[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) has_b[nt] = n0 + nt * 8 + g < N;
 #pragma unroll
     for (int h = 0; h < NB; ++h)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const int n = n0 + nt * 8 + g;
-            b_row[h][nt] = n < N ? w + ((long long)h * N + n) * K : nullptr;
-        }
+        for (int nt = 0; nt < NT; ++nt)
+            b_row[h][nt] = w + ((long long)h * N + (has_b[nt] ? n0 + nt * 8 + g : 0)) * K;
     float acc[NB][NT][4];
 #pragma unroll
     for (int h = 0; h < NB; ++h)
@@ -462,14 +477,20 @@ __global__ void __launch_bounds__(kThreadsG) grouped_few_rows_bf16_kernel(const 
         for (int u = 0; u < U; ++u) {
             const int s = s0 + 4 * u;
             const int k = s * 32 + t4 * 8;
-            const bool in = s < steps;
-            av[u][0] = in && a_lo ? *reinterpret_cast<const uint4*>(a_lo + k) : zero;
-            av[u][1] = in && a_hi ? *reinterpret_cast<const uint4*>(a_hi + k) : zero;
+            if (s < steps) {            // the same for all lanes of the warp
 #pragma unroll
-            for (int h = 0; h < NB; ++h)
+                for (int h = 0; h < NB; ++h)
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                    bv[u][h][nt] = in && b_row[h][nt] ? *reinterpret_cast<const uint4*>(b_row[h][nt] + k) : zero;
+                    for (int nt = 0; nt < NT; ++nt) bv[u][h][nt] = load_stream16(b_row[h][nt] + k);
+                av[u][0] = load_stream16(a_lo + k);
+                av[u][1] = load_stream16(a_hi + k);
+            } else {
+#pragma unroll
+                for (int h = 0; h < NB; ++h)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) bv[u][h][nt] = zero;
+                av[u][0] = av[u][1] = zero;
+            }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
