@@ -744,10 +744,10 @@ B200_EXPORT int b200_grouped_gemm(const void* a, const void* w, void* c, const i
     p.c_group = c_group; p.act_limit = limit; p.act_slope = slope; p.act_offset = offset;
     p.act_kind = gated == 2 ? 1 : 0;
     const dim3 grid((unsigned)tiles, n_tiles);
-    const int all_rows = offsets ? list_rows : rows * groups;
-    const bool overlap = (offsets ? list_rows : rows) <= kOverlapMostRows;
-    // Few rows in all: the stream of the matrices sets the time, and the kernel of many small blocks serves.
-    if (dtype == 1 && all_rows <= kFewRowsMost * (offsets ? 1 : groups) && K % 32 == 0 && lda % 8 == 0 && a_group % 8 == 0
+    const int most_rows = offsets ? list_rows : rows;       // of all lists; of every group without lists
+    const bool overlap = most_rows <= kOverlapMostRows;
+    // Few rows: the stream of the matrices sets the time, and the kernel of many small blocks serves.
+    if (dtype == 1 && most_rows <= kFewRowsMost && K % 32 == 0 && lda % 8 == 0 && a_group % 8 == 0
         && (((uintptr_t)a | (uintptr_t)w) & 15) == 0) {
         const long long few_tiles = offsets ? (long long)list_rows / kFM + groups : (long long)groups * ((rows + kFM - 1) / kFM);
         const dim3 few_grid((unsigned)few_tiles, (N + kFN - 1) / kFN);
