@@ -532,3 +532,74 @@ def test_replay_program(folders, references, tmp_path, dtype):
         assert at == data.shape[0]
     compare({rid: torch.cat(rows) for rid, rows in results.items()},
             {rid: expected[rid][:lengths[rid]] for rid in sequences}, dtype, f"replay program/{dtype}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(6, 3, 20, 36, 37), (4, 2, 64, 64, 40), (8, 1, 128, 128, 300), (3, 3, 64, 64, 1)])
+def test_grouped_attention_with_unit_norm_at_the_edges_of_its_window(dtype, shape):
+    """Keys and values of their own, grouped heads, queries and keys divided by their root mean square
+    without a weight, a window, no sink, no positions.  A request that decodes one token over 700 keys, one
+    whose last 35 tokens over scattered pages are this step's portion, one that starts.  Queries point at the
+    oldest key inside the window and at the one just outside it, for tokens of the portion and for the token
+    decoded alone, and at keys on both sides of a page border."""
+    from vllm_from_scratch_b200 import kernels
+    g = torch.Generator().manual_seed(13)
+    H, G, d, dv, window = shape
+    page, eps, scale = 16, 1e-5, 8.0 / d           # a pointed query scores 8, the others about 8 / sqrt(d)
+    lengths, fresh = [700, 333, 5], [1, 35, 5]
+    sequences = []
+    for n in lengths:
+        q, k, v = torch.randn(n, H, d, generator=g), torch.randn(n, G, d, generator=g), torch.randn(n, G, dv, generator=g)
+        sequences.append([q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double()])
+
+    def point(sequence, at, key):          # the direction survives the unit norm
+        q, k, _ = sequence
+        if 0 <= key <= at:
+            for head in range(H):
+                q[at, head] = k[key, head // (H // G)].clone()
+
+    point(sequences[0], 699, 699 - window + 1)
+    for at, key in {320: 320 - window + 1, 321: 321 - window, 322: 319, 323: 320, 324: 304, 325: 303, 332: 332 - window}.items():
+        point(sequences[1], at, key)
+    tokens = sum(fresh)
+    qkv = torch.zeros(tokens, H * d + G * d + G * dv, dtype=torch.float64)
+    want = torch.zeros(tokens, H * dv, dtype=torch.float64)
+    row, starts, slots, positions = 0, [0], [], []
+    orders, base = [], 0
+    for n in lengths:
+        count = -(-n // page)
+        orders.append([base + p for p in torch.randperm(count, generator=g).tolist()])
+        base += count
+    k_pool = torch.zeros(base, G, page, d, dtype=dtype)
+    v_pool = torch.zeros(base, G, page, dv, dtype=dtype)
+    for (q, k, v), n, new, order in zip(sequences, lengths, fresh, orders):
+        k_unit = plain.rms(k, eps).to(dtype).double()          # the cache holds rounded rows
+        for position in range(n):
+            spot = (order[position // page], slice(None), position % page)
+            if position < n - new:
+                k_pool[spot], v_pool[spot] = k_unit[position].to(dtype), v[position].to(dtype)
+        for position in range(n - new, n):
+            qkv[row] = torch.cat([q[position].reshape(-1), k[position].reshape(-1), v[position].reshape(-1)])
+            slots.append(order[position // page] * page + position % page)
+            positions.append(position)
+            q_unit = plain.rms(q[position], eps).to(dtype).double()
+            seen = list(plain.visible(position, window))
+            for head in range(H):
+                kv = head // (H // G)
+                weights = plain.softmax_with_sink((k_unit[seen, kv] @ q_unit[head]) * scale)
+                want[row, head * dv:(head + 1) * dv] = weights @ v[seen, kv]
+            row += 1
+        starts.append(row)
+    width = max(len(o) for o in orders)
+    table = torch.full((len(lengths), width), -1, dtype=torch.int32)
+    for r, order in enumerate(orders):
+        table[r, :len(order)] = torch.tensor(order, dtype=torch.int32)
+    k_d, v_d = dev(k_pool), dev(v_pool)
+    q_out = torch.empty(tokens, H * d, dtype=dtype, device="cuda")
+    kernels.head_norm_scale_cache(dev(qkv, dtype), i32(positions), i32(slots), None, None, eps, None, q_out, k_d, v_d,
+                                  H, G, d, dv, page, unit_norm=True)
+    out = torch.empty(tokens, H * dv, dtype=dtype, device="cuda")
+    kernels.biased_paged_attention(q_out, k_d, v_d, out, i32(starts), i32(lengths), dev(table), None, H, G, d, dv, page,
+                                   scale, window, max(fresh), max(lengths), 1)
+    tol = 2e-5 if dtype == torch.float32 else 4e-2
+    assert torch.allclose(out.cpu().double(), want, atol=tol, rtol=tol), float((out.cpu().double() - want).abs().max())
