@@ -105,13 +105,14 @@ __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const bf16* _
             offset = page_shift >= 0 ? kp & (page_size - 1) : kp - index * page_size;
             page = table[index];
         }
+        // v_s == k_s: the rows serve as keys and as values, and one tile holds both
         if (page >= 0) {
             const size_t at = (size_t)page * page_stride + in_page + (size_t)offset * D;
             cp_async16(k_s + at_s, k_pages + at);
-            cp_async16(v_s + at_s, v_pages + at);
+            if (v_s != k_s) cp_async16(v_s + at_s, v_pages + at);
         } else {
             *reinterpret_cast<uint4*>(k_s + at_s) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(v_s + at_s) = make_uint4(0, 0, 0, 0);
+            if (v_s != k_s) *reinterpret_cast<uint4*>(v_s + at_s) = make_uint4(0, 0, 0, 0);
         }
     }
 }
@@ -155,7 +156,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
     const int* __restrict__ seq_lens, const int* __restrict__ block_table, int max_pages, int nq,
     int nkv, int page_size, float scale_log2, int window, int splits, const float* __restrict__ slopes,
-    const float* __restrict__ sinks, int cache_nkv) {
+    const float* __restrict__ sinks, int cache_nkv, int one_tile) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);
     overlap_trigger();
@@ -194,8 +195,13 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
         if (row_b < group) slope_b = slopes[kv_head * group + row_b] * kLog2e;
     }
 
-    auto k_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D; };
-    auto v_stage = [&](int s) { return stage_base + (size_t)s * 2 * kKeys * D + kKeys * D; };
+    // one_tile (the launcher's choice, only where the values are the keys themselves: one pointer for both
+    // operands): the rows are fetched once and a stage is one tile; the block then takes half the shared
+    // memory, and three blocks fit on an SM where one did at rows of 256.
+    const size_t value_tile = one_tile ? 0 : (size_t)kKeys * D;
+    const size_t stage_size = (size_t)kKeys * D + value_tile;
+    auto k_stage = [&](int s) { return stage_base + (size_t)s * stage_size; };
+    auto v_stage = [&](int s) { return stage_base + (size_t)s * stage_size + value_tile; };
 
     if (tiles > 0) {
         load_kv_tile<D>(k_stage(0), v_stage(0), k_pages, v_pages, table, my_begin, my_end, cache_head, cache_nkv, page_size, page_shift);
@@ -604,13 +610,21 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
                   int cache_nkv = 0) {
     auto kernel = decode_attention_kernel<D, EXACT>;
     if (cache_nkv <= 0) cache_nkv = nkv;
-    const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
+    // two stages of a key tile and a value tile; of one tile where the values are the keys themselves, but
+    // room for the warps' partial results ([4][16][D] floats and their statistics) at the end in any case
+    // One tile pays where the launch has more blocks than the GPU has SMs, so that more of them run at a time
+    // (64 requests over rows of 256: 46.8 against 72.5 us); for a launch that finds room anyway it gains nothing
+    // (8 requests: 24.0 against 23.3 us) and a whole decode step was slower with it (0.566 against 0.509 ms).
+    const bool one_tile = EXACT && k_pages == v_pages && (long long)splits * nkv * num_requests > sm_count();
+    const int smem = one_tile ? 4 * 16 * D * (int)sizeof(float) + 4 * 16 * 2 * (int)sizeof(float)
+                              : 2 * 2 * kKeys * D * (int)sizeof(bf16);
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (status != cudaSuccess) return fail("decode_attention", cudaGetErrorString(status));
     dim3 grid(splits, nkv, num_requests);
     launch_overlapped(kernel, grid, kThreads, smem, stream,
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, partial_o, partial_ml,
-        seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits, slopes, sinks, cache_nkv);
+        seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits, slopes, sinks, cache_nkv,
+        one_tile ? 1 : 0);
     if (int rc = check_launch("decode_attention")) return rc;
     if (splits > 1) {
         launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,
