@@ -91,11 +91,27 @@ LZ_E = {
     ],
 }
 
-CONFIGS = {"A": (LZ_A, 16), "B": (LZ_B, 16), "C": (LZ_C, 4), "D": (LZ_D, 32), "E": (LZ_E, 16)}
+# Keys and values of 256 on the tensor-core kernels, latent rows of 48 (the float32-arithmetic kernel) under
+# 16 and 20 heads, 32 experts of which 8 are chosen from 4 of 8 groups, one expert chosen from one group of
+# two, a width that is no multiple of 128, readers with longer windows than their owners.
+LZ_F = {
+    "architecture": "Lobuzen", "vocab": 1000, "width": 320, "norm": {"eps": 1e-6}, "token_side": {"dim": 40},
+    "layers": [
+        _latent(16, 64, 64, 48, 0.125, 90, _moe(200, 32, 8, 8, 4)),
+        _attention(16, 4, 256, 256, 0.0625, 64, _moe(72, 32, 8, 8, 4)),
+        _attention(8, 8, 128, 128, 0.09, 33, _dense(200, 4.0)),
+        _latent(20, 32, 48, 48, 0.18, 128, _dense(520, 0.5), kv_from=0),
+        _latent(8, 32, 48, 256, 0.18, 40, _moe(64, 6, 1, 3, 1)),
+        _latent(8, 24, 40, 256, 0.2, 100, None, kv_from=4),
+    ],
+}
+
+CONFIGS = {"A": (LZ_A, 16), "B": (LZ_B, 16), "C": (LZ_C, 4), "D": (LZ_D, 32), "E": (LZ_E, 16), "F": (LZ_F, 16)}
 LENGTHS = {
     "A": {"a": 70, "b": 45, "c": 100, "d": 37, "e": 64, "f": 1, "g": 150},
     "B": {"a": 70, "b": 33, "c": 130, "d": 2, "e": 64, "g": 200},
     "C": {"a": 41, "b": 2, "c": 23, "g": 70},
     "D": {"a": 70, "b": 1, "c": 140, "g": 230},
     "E": {"a": 300, "b": 64, "c": 129, "g": 260},
+    "F": {"a": 150, "b": 65, "c": 17, "g": 120},
 }

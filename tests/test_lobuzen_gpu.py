@@ -21,14 +21,21 @@ F32_REL, BF16_REL = 2e-5, 0.06
 
 
 def steady_choice(weights, raw):
-    """Corrections two apart from expert to expert, in a shuffled order of their own in every layer: no
-    sigmoid can bridge that, so the choice of experts never hangs on a close call between two scores,
-    while the weights of the chosen still differ from token to token."""
+    """Corrections two apart from expert to expert within a group and a hundred apart from group to group,
+    both in a shuffled order of their own in every layer: no sigmoid can bridge that, so neither the choice of
+    groups (by the sum of two choice scores) nor the choice of experts ever hangs on a close call between two
+    scores, while the weights of the chosen still differ from token to token."""
     generator = torch.Generator().manual_seed(99)
     for name, tensor in weights.items():
-        if name.endswith(".correction"):
-            levels = 2.0 * torch.randperm(tensor.shape[0], generator=generator).float() - tensor.shape[0]
-            weights[name] = levels.to(tensor.dtype)
+        if not name.endswith(".correction"):
+            continue
+        router = raw["layers"][int(name.split(".")[0][1:])]["mlp"]["router"]
+        experts = tensor.shape[0]
+        count = (router.get("groups") or {"count": 1})["count"]
+        per = experts // count
+        group_level = 100.0 * torch.randperm(count, generator=generator).float()
+        levels = torch.cat([group_level[g] + 2.0 * torch.randperm(per, generator=generator).float() for g in range(count)])
+        weights[name] = (levels - levels.mean().round()).to(tensor.dtype)
 
 
 @pytest.fixture(scope="module")
